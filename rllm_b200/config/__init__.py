@@ -1,7 +1,8 @@
 from .base import (Architecture, ConfigError, ModelConfig, config_from_dict, load_config,
                    register_architecture, registered_architectures, resolve_architecture)
 from .llama import LlamaConfig, RopeScaling
+from .zukotar import GLAConfig, LatentAttentionConfig, MoEConfig, ZukotarConfig
 
 __all__ = ["Architecture", "ConfigError", "ModelConfig", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "resolve_architecture",
-           "LlamaConfig", "RopeScaling"]
+           "LlamaConfig", "RopeScaling", "GLAConfig", "LatentAttentionConfig", "MoEConfig", "ZukotarConfig"]

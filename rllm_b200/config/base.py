@@ -1,6 +1,7 @@
 """Typed model configuration and the one registry from architecture name to model.
 
-A `config.json` names its architecture (`architectures[0]`, else `model_type`);
+A `config.json` names its architecture (`architectures[0]` or the string `architecture`, else
+`model_type`);
 the registry maps that name to a typed configuration class and to the function
 that builds the model from it. Parity: the reference's serde `ModelConfig`
 (src/model/config.rs:332-612), `ModelArch::from_model_type`
@@ -60,7 +61,9 @@ def registered_architectures() -> list[str]:
 
 
 def resolve_architecture(raw: dict[str, Any]) -> Architecture:
-    names = raw.get("architectures") or []
+    names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):        # designs that name themselves with one string
+        names.append(raw["architecture"])
     for n in names:
         if n in _REGISTRY:
             return _REGISTRY[n]

@@ -6,10 +6,11 @@
 using namespace rllm;
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] = table[ids[t], :]  (reference: src/gpu/cuda/shaders/embed.cu:24-59)
+// out[t, :] = table[ids[t], :] * scale  (reference: src/gpu/cuda/shaders/embed.cu:24-59; the factor is 1 for
+// models that do not scale their embedding, the product is taken in float)
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                             float* __restrict__ out, int H, int V, int* __restrict__ err) {
+                             float* __restrict__ out, int H, int V, int* __restrict__ err, float scale) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
@@ -20,17 +21,17 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
     return;
   }
   const TW* row = table + (size_t)id * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = to_f32(row[i]) * scale;
 }
 
 RLLM_API int rllm_embed(const int* ids, const void* table, int table_dt, float* out, int T, int H,
-                        int V, int* err, void* stream) {
+                        int V, int* err, float scale, void* stream) {
   if (T <= 0) return 0;
   const int threads = H >= 256 ? 256 : (H >= 128 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
   int rc = 0;
-  if (table_dt == DT_F32) rc = launch_ex(embed_kernel<float>, dim3(T), dim3(threads), 0, s, 1, ids, (const float*)table, out, H, V, err);
-  else if (table_dt == DT_BF16) rc = launch_ex(embed_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, ids, (const bf16*)table, out, H, V, err);
+  if (table_dt == DT_F32) rc = launch_ex(embed_kernel<float>, dim3(T), dim3(threads), 0, s, 1, ids, (const float*)table, out, H, V, err, scale);
+  else if (table_dt == DT_BF16) rc = launch_ex(embed_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, ids, (const bf16*)table, out, H, V, err, scale);
   else return ERR_BAD_DTYPE;
   return rc;
 }

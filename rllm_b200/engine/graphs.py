@@ -110,12 +110,18 @@ class DecodeGraphs:
         return slot
 
     def _capture(self, slot: _Slot) -> None:
-        # once launch by launch (this also sets every kernel's attributes), then captured
+        # once launch by launch (this also sets every kernel's attributes), then captured. That first
+        # run is in addition to the replay that follows it: it goes without state slots (-1: a mixer
+        # with a recurrent state then starts from zero and keeps nothing), so that a state that moves
+        # with every token is moved once per step; writing the same keys twice changes nothing.
         cur = torch.cuda.current_stream(self.engine.device)
         side = torch.cuda.Stream(self.engine.device)
         side.wait_stream(cur)
+        S = slot.lay.S
         with torch.cuda.stream(side):
+            slot.lay.view(slot.dev, 5, S).fill_(-1)
             self._forward(slot)
+            slot.lay.view(slot.dev, 5, S).copy_(slot.lay.view(slot.host, 5, S), non_blocking=True)
         cur.wait_stream(side)
         torch.cuda.synchronize(self.engine.device)
         if self.pool is None:

@@ -51,8 +51,8 @@ class Backend:
             sm100.init(self.device)
 
     # ---- element-wise / row-wise
-    def embed(self, ids, table, err=None):
-        return ops.embed(ids, table, err=err)
+    def embed(self, ids, table, err=None, scale=1.0):
+        return ops.embed(ids, table, err=err, scale=scale)
 
     def rmsnorm(self, x, w, eps, out_dtype=None, rows=None):
         return ops.rmsnorm(x, w, eps, out_dtype or self.dtype, rows=rows)
@@ -88,7 +88,8 @@ class Backend:
 
     # ---- matrix products: y = x W^T
     def _tc(self, x, w):
-        return self._sm100 is not None and self._sm100.gemm_supported(x, w)
+        # weights whose height is no multiple of 4 (a gate row per head, say) stay on the CUDA cores
+        return self._sm100 is not None and w.shape[0] % 4 == 0 and self._sm100.gemm_supported(x, w)
 
     def linear(self, x, w, bias=None):
         if bias is None and self._fused_norm(x, w):
@@ -176,6 +177,56 @@ class Backend:
                 return out
         return ops.paged_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions,
                                         cache.block_table, nh, scale, window)
+
+    # ---- mixers with a cache of latents or a recurrent state, routed feed-forwards (library "mix")
+    @property
+    def _mix(self):
+        from . import mix
+        return mix
+
+    def rmsnorm_add(self, residual, y, w, eps):
+        """residual += rmsnorm(y) * w (y [T, H], or [T, parts, H] summed over parts first), in float."""
+        return self._mix.rmsnorm_add(residual, y, w, eps)
+
+    def add_row(self, h, v):
+        return self._mix.add_row(h, v)
+
+    def linear_heads(self, a, a_gs, w, out, c_gs, f32=False, gate=None):
+        """One product per head in one launch: out[:, g*c_gs + n] = a[:, g*a_gs : g*a_gs + K] w[g]^T."""
+        return self._mix.grouped_gemm_uniform(a, a_gs, w, out, c_gs,
+                                              self._mix.GEPI_STORE_F32 if f32 else self._mix.GEPI_STORE, gate=gate)
+
+    def route(self, logits, top, groups=1, keep=1, renorm=False):
+        """Router logits -> the plan of the experts' grouped products (all on the device)."""
+        idx, wt = self._mix.moe_topk(logits, top, groups, keep, renorm)
+        return idx, wt, self._mix.moe_plan(idx, wt, logits.shape[1])
+
+    def experts_up(self, x, w_up, plan, act="relu2"):
+        """act(x[token of row] W_up[expert of row]^T) for every sorted row of the plan."""
+        if act != "relu2":
+            raise ops.KernelError(f"expert activation {act!r} has no kernel")
+        out = torch.empty((plan.n_rows, w_up.shape[1]), dtype=x.dtype, device=x.device)
+        return self._mix.grouped_gemm_ragged(x, w_up, plan, out, self._mix.GEPI_RELU2, gather=True)
+
+    def experts_down(self, a, w_down, plan, T, top):
+        """weight of row * (a[row] W_down[expert of row]^T), stored at the row's (token, slot): float
+        [T, top, width], every place written exactly once."""
+        out = torch.empty((T * top, w_down.shape[1]), dtype=torch.float32, device=a.device)
+        self._mix.grouped_gemm_ragged(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=True)
+        return out.view(T, top, w_down.shape[1])
+
+    def latent_prepare(self, *a, **k):
+        return self._mix.latent_prepare(*a, **k)
+
+    def latent_attention(self, qfull, cache, ctx, rank, scale, window):
+        return self._mix.latent_attention(qfull, cache.tensors["kv"], ctx.token_seq, ctx.positions,
+                                          cache.block_table, rank, scale, window)
+
+    def gla_scan(self, *a, **k):
+        return self._mix.gla_scan(*a, **k)
+
+    def gla_finish(self, *a, **k):
+        return self._mix.gla_finish(*a, **k)
 
     # ---- selection
     def argmax(self, logits):

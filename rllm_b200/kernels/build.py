@@ -25,10 +25,13 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 
 # library name -> sources. "simt" holds the generic kernels of both precisions;
 # "sm100" the tcgen05/TMA kernels that only the bfloat16 path calls; "host" the native
-# bookkeeping of the cache manager (plain C++, no device code).
+# bookkeeping of the cache manager (plain C++, no device code); "mix" the mixers and feed-forwards
+# beyond grouped-query attention and SwiGLU (latent attention, gated linear attention, routed experts),
+# both precisions, built only when a model uses them.
 LIBRARIES: dict[str, list[str]] = {
     "simt": ["simt_basic.cu", "simt_gemm.cu", "simt_attention.cu", "sampling.cu"],
     "sm100": ["tc_gemm.cu", "stream_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu", "wait_probe.cu"],
+    "mix": ["grouped_gemm.cu", "moe_route.cu", "latent_attention.cu", "gla.cu"],
     "host": ["host_runtime.cpp"],          # no CUDA: the cache manager's bookkeeping and metadata writer
 }
 

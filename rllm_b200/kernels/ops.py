@@ -29,7 +29,7 @@ class KernelError(RuntimeError):
 _P = c_void_p
 _SIGS = {
     "simt": {
-        "rllm_embed": [_P, _P, c_int, _P, c_int, c_int, c_int, _P, _P],
+        "rllm_embed": [_P, _P, c_int, _P, c_int, c_int, c_int, _P, c_float, _P],
         "rllm_rmsnorm": [_P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, _P],
         "rllm_rope_table": [_P, _P, _P, c_int, c_int, _P],
         "rllm_rope_cache_write": [_P, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
@@ -112,8 +112,8 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 # ---------------------------------------------------------------------------------------------
 
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None,
-          err: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = table[ids[t]] as float32. ids int32 [T]; table [V, H] float32/bfloat16."""
+          err: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale as float32. ids int32 [T]; table [V, H] float32/bfloat16."""
     _cuda(ids, "ids"); _cuda(table, "table")
     if ids.dtype != torch.int32 or ids.dim() != 1 or not ids.is_contiguous():
         raise KernelError("ids must be a contiguous int32 vector")
@@ -123,7 +123,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = Non
     if out is None:
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     _check(_fn("simt", "rllm_embed")(ids.data_ptr(), table.data_ptr(), _dt(table, "table"),
-                                     out.data_ptr(), T, H, V, _ptr(err), _stream()), "embed")
+                                     out.data_ptr(), T, H, V, _ptr(err), float(scale), _stream()), "embed")
     return out
 
 

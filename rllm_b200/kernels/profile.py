@@ -100,9 +100,9 @@ class OpProfile:
         return out
 
     # ---- the backend's operations
-    def embed(self, ids, table, err=None):
+    def embed(self, ids, table, err=None, scale=1.0):
         return self._timed("embed", ids.numel() * table.shape[1] * (table.element_size() + 4), 0,
-                           self._be.embed, ids, table, err=err)
+                           self._be.embed, ids, table, err=err, scale=scale)
 
     def rmsnorm(self, x, w, eps, out_dtype=None, rows=None):
         T = x.shape[0] if rows is None else rows.numel()

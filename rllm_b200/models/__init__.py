@@ -1,4 +1,5 @@
 from .model import LayerCall, Model
 from . import llama  # registers LlamaForCausalLM
+from . import zukotar  # registers Zukotar
 
-__all__ = ["LayerCall", "Model", "llama"]
+__all__ = ["LayerCall", "Model", "llama", "zukotar"]

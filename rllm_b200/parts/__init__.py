@@ -2,14 +2,18 @@ from .base import (CacheKind, KVCacheSpec, LayerCache, Param, Part, Source, Stat
                    make_part, register_cache_kind, register_part, registered_parts)
 from .rope_rules import register_rope_rule, registered_rope_rules
 from .norm import RMSNorm
-from .rope import RotaryEmbedding, inverse_frequencies
+from .rope import InterleavedRotary, RotaryEmbedding, inverse_frequencies
 from .attention import GQAttention
 from .ffn import SwiGLU
-from .block import PreNormBlock
+from .block import LoopStep, PreNormBlock, SandwichBlock
+from .latent_attention import LatentAttention, LatentCacheSpec
+from .gla import GatedLinearAttention
+from .moe import RoutedExperts
 from .embedding import Embedding, OutputHead
 
 __all__ = ["CacheKind", "cache_kind_of", "register_cache_kind", "register_rope_rule", "registered_rope_rules",
            "KVCacheSpec", "LayerCache", "Param", "Part", "Source", "StateSpec", "make_part",
            "register_part", "registered_parts", "RMSNorm", "RotaryEmbedding",
            "inverse_frequencies", "GQAttention", "SwiGLU", "PreNormBlock", "Embedding",
-           "OutputHead"]
+           "OutputHead", "InterleavedRotary", "SandwichBlock", "LoopStep", "LatentAttention",
+           "LatentCacheSpec", "GatedLinearAttention", "RoutedExperts"]

@@ -1,8 +1,11 @@
 """How a layer's parts are arranged. Pre-norm residual block, the reference's Llama layer
-order (src/model/registry/llama.rs:163-245): h += mixer(norm(h)); h += ffn(norm(h))."""
+order (src/model/registry/llama.rs:163-245): h += mixer(norm(h)); h += ffn(norm(h)).
+`SandwichBlock` norms each sublayer's output as well: h += norm_b(mixer(norm(h))), the same for
+the feed-forward, which may be absent. `LoopStep` is a block that only adds a learned vector to
+every row: what a pass of a looped stretch of layers begins with."""
 from __future__ import annotations
 
-from .base import Part, register_part
+from .base import Param, Part, Source, register_part
 
 
 class PreNormBlock(Part):
@@ -43,4 +46,84 @@ class PreNormBlock(Part):
         return norm.forward(h, ctx)
 
 
+class SandwichBlock(Part):
+    """A norm before and after each sublayer. The post-norm, the sum over a routed feed-forward's
+    parts and the residual sum are one float kernel. `names`: checkpoint sub-prefixes of mixer and
+    feed-forward; the four norms' weights are tensors named `norm_names` under the block's prefix."""
+    graph_safe = True
+
+    def __init__(self, mixer_norm: Part, mixer: Part, mixer_post: Part, ffn_norm: Part | None = None,
+                 ffn: Part | None = None, ffn_post: Part | None = None, names=("mix.", "mlp.")):
+        self.mixer_norm, self.mixer, self.mixer_post = mixer_norm, mixer, mixer_post
+        self.ffn_norm, self.ffn, self.ffn_post = ffn_norm, ffn, ffn_post
+        self.names = names
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn, self.ffn_post)
+                if p is not None]
+
+    def set_prefix(self, prefix: str):
+        self.prefix = prefix
+        for norm in (self.mixer_norm, self.mixer_post, self.ffn_norm, self.ffn_post):
+            if norm is not None:
+                norm.prefix = prefix            # a norm's tensor is named by its `weight_name`
+        for part, sub in ((self.mixer, self.names[0]), (self.ffn, self.names[1])):
+            if part is not None:
+                part.prefix = prefix + sub
+                for c in part.children():
+                    if not c.prefix:
+                        c.prefix = part.prefix
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, h, ctx, cache):
+        """h: float32 residual stream [T, hidden], updated in place."""
+        be = ctx.backend
+        x = PreNormBlock._norm(self.mixer_norm, self.mixer, h, ctx)
+        be.rmsnorm_add(h, self._output(self.mixer, h, x, ctx, cache), self.mixer_post.weight_f32(), self.mixer_post.eps)
+        if self.ffn is not None:
+            x = PreNormBlock._norm(self.ffn_norm, self.ffn, h, ctx)
+            be.rmsnorm_add(h, self._output(self.ffn, h, x, ctx), self.ffn_post.weight_f32(), self.ffn_post.eps)
+        return h
+
+    @staticmethod
+    def _output(part, h, x, ctx, *cache):
+        """The sublayer's float output: returned by parts that can (`returns_output`), else gathered
+        in a zeroed buffer that stands in for the residual stream."""
+        if getattr(part, "returns_output", False):
+            return part.forward(x, ctx, *cache, None)
+        import torch
+        y = torch.zeros_like(h)
+        part.forward(x, ctx, *cache, y)
+        return y
+
+
+class LoopStep(Part):
+    """h += table[index] on every row. The passes of one loop share the table [times, hidden]: the
+    first owns the tensor (`owner` None), the others name the first."""
+    graph_safe = True
+
+    def __init__(self, hidden: int, times: int, index: int, owner: "LoopStep | None" = None, name: str = "step"):
+        self.hidden, self.times, self.index, self.owner, self.name = hidden, times, index, owner, name
+        self.table = None
+
+    def params(self):
+        if self.owner is not None:
+            return []
+        return [Param("table", (Source(self.name, (self.times, self.hidden)),), role="vector")]
+
+    def cache_spec(self):
+        return None
+
+    def finalize(self, device, dtype):
+        table = (self.owner or self).table
+        self._row = table[self.index].float().contiguous()
+
+    def forward(self, h, ctx, cache=None):
+        return ctx.backend.add_row(h, self._row)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)
+register_part("block", "loop_step", LoopStep)

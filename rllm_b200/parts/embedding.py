@@ -1,5 +1,5 @@
-"""Token embedding and output head. Embedding is a row copy with no scaling
-(src/gpu/cuda/shaders/embed.cu:24-59); the head is final norm, then a product with
+"""Token embedding and output head. Embedding is a row copy (src/gpu/cuda/shaders/embed.cu:24-59),
+times `scale` for designs that scale it (1 otherwise; a head tied to the table uses the table itself); the head is final norm, then a product with
 `lm_head.weight`, or with the embedding table when the two are tied
 (src/model/primitives.rs:124-143, 1467; src/model/loader/mod.rs:693-702). Logits are
 float32 and are computed only for the rows that were asked for."""
@@ -11,15 +11,17 @@ from .base import Param, Part, Source, register_part
 class Embedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab: int, hidden: int, name: str = "embed_tokens.weight"):
-        self.vocab, self.hidden, self.name = vocab, hidden, name
+    def __init__(self, vocab: int, hidden: int, name: str = "embed_tokens.weight", scale: float = 1.0):
+        self.vocab, self.hidden, self.name, self.scale = vocab, hidden, name, float(scale)
         self.table = None
 
     def params(self):
         return [Param("table", (Source(self.name, (self.vocab, self.hidden)),))]
 
     def forward(self, ctx):
-        return ctx.backend.embed(ctx.token_ids, self.table, err=ctx.extras.get("err_flag"))
+        if self.scale == 1.0:
+            return ctx.backend.embed(ctx.token_ids, self.table, err=ctx.extras.get("err_flag"))
+        return ctx.backend.embed(ctx.token_ids, self.table, err=ctx.extras.get("err_flag"), scale=self.scale)
 
 
 class OutputHead(Part):

@@ -1,0 +1,47 @@
+"""A routed feed-forward (mixture of experts) as a part.
+
+Router logits z = W_router h in float (h in the run dtype), scores s = softmax(z) over all experts.
+The experts form `groups` equal groups of neighbours; a group's score is its largest; only experts of
+the best `keep` groups can be chosen; of those the `top` largest scores are taken, with the scores
+themselves as weights (`renorm`: divided by their sum). An expert is W_down act(W_up h) without
+biases, act = relu(.)^2. The experts of all tokens run as two grouped products over a row list
+sorted by expert that a small kernel writes on the device, so the launches depend on the step's
+size only; the weighted outputs land in one float row per (token, chosen expert), which the
+caller sums in slot order (`SandwichBlock` does it inside its norm).
+"""
+from __future__ import annotations
+
+from .base import Param, Part, Source, register_part
+
+
+class RoutedExperts(Part):
+    graph_safe = True
+    returns_output = True
+
+    def __init__(self, hidden: int, ff: int, experts: int, top: int, groups: int = 1, keep: int = 1,
+                 renorm: bool = False, act: str = "relu2"):
+        self.hidden, self.ff, self.experts, self.top = hidden, ff, experts, top
+        self.groups, self.keep, self.renorm, self.act = groups, keep, renorm, act
+        self.w_router = self.w_up = self.w_down = None
+
+    def params(self):
+        E, W, F = self.experts, self.hidden, self.ff
+        return [Param("w_router", (Source("router", (E, W)),)),
+                Param("w_up", tuple(Source(f"e{e}.up", (F, W)) for e in range(E))),
+                Param("w_down", tuple(Source(f"e{e}.down", (W, F)) for e in range(E)))]
+
+    def finalize(self, device, dtype):
+        self._up = self.w_up.view(self.experts, self.ff, self.hidden)
+        self._down = self.w_down.view(self.experts, self.hidden, self.ff)
+
+    def forward(self, x, ctx, residual=None):
+        """-> float [T, top, hidden]: the chosen experts' weighted outputs, to be summed over dim 1."""
+        if residual is not None:
+            raise NotImplementedError("RoutedExperts returns its parts; the block sums them")
+        be = ctx.backend
+        x = x.tensor() if hasattr(x, "tensor") else x
+        _, _, plan = be.route(be.linear_f32(x, self.w_router), self.top, self.groups, self.keep, self.renorm)
+        return be.experts_down(be.experts_up(x, self._up, plan, self.act), self._down, plan, x.shape[0], self.top)
+
+
+register_part("ffn", "moe", RoutedExperts)

@@ -24,6 +24,15 @@ class RMSNorm(Part):
         own first product: a tensor, or the backend's deferred form that its products accept."""
         return ctx.backend.normed(h, self.weight, self.eps, rows)
 
+    def weight_f32(self):
+        """The weight as float32 (kernels that norm in float throughout take it so); made once."""
+        if getattr(self, "_w32", None) is None:
+            self._w32 = self.weight.float().contiguous()
+        return self._w32
+
+    def finalize(self, device, dtype):
+        self._w32 = None            # weights were (re)bound
+
     def forward_f32(self, h, ctx):
         import torch
         return ctx.backend.rmsnorm(h, self.weight, self.eps, out_dtype=torch.float32)

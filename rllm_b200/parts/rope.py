@@ -54,4 +54,32 @@ class RotaryEmbedding(Part):
                                      self.head_dim, self.rot_dim, ctx=ctx, key=self.table_key)
 
 
+class InterleavedRotary(Part):
+    """Rotates pairs (2i, 2i+1), i < dims/2, of a vector of `rot_dim` numbers by position * f_i with
+    f_i = base^(-2i/dims); the dimensions from `dims` on pass unchanged. The part owns the rule (the
+    frequencies and the step's table of cos and sin); the rotation itself runs inside the kernel of
+    the mixer that uses it."""
+    graph_safe = True
+
+    def __init__(self, rot_dim: int, base: float, dims: int | None = None):
+        self.rot_dim = rot_dim
+        self.dims = rot_dim if dims is None else dims
+        if self.dims % 2 or self.dims > rot_dim:
+            raise ValueError(f"rotated dimensions {self.dims} must be even and <= {rot_dim}")
+        self.base = float(base)
+        self.inv_freq = None
+        self.table_key = ("rope_interleaved", self.dims, self.base)
+
+    def finalize(self, device, dtype):
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        self.inv_freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
+
+    def table(self, ctx):
+        """float32 [T, dims/2, 2] (cos, sin) for the step's tokens, shared by the layers of one rule."""
+        if self.dims == 0:
+            return torch.empty((ctx.num_tokens, 0, 2), dtype=torch.float32, device=self.inv_freq.device)
+        return ctx.backend.rope_table(ctx, ctx.positions, self.inv_freq, self.dims, self.table_key)
+
+
 register_part("position", "rope", RotaryEmbedding)
+register_part("position", "rope_interleaved", InterleavedRotary)

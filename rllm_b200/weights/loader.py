@@ -77,7 +77,8 @@ def load_weights(model, model_dir: str, dtype: torch.dtype, device) -> None:
             ent = store.entries.get(n)
             if ent is None:
                 continue
-            if tuple(ent.shape) != tuple(s.shape):
+            # a size of -1 in a declared shape is one that only the checkpoint knows
+            if len(ent.shape) != len(s.shape) or any(w != -1 and w != g for w, g in zip(s.shape, ent.shape)):
                 wrong_shape.append((n, s.shape, ent.shape))
             floating = ent.dtype in ("F32", "BF16", "F16", "F64")
             if (p.role == "table") == floating:

@@ -15,6 +15,9 @@ from .safetensors_io import write_safetensors
 
 
 def _fill(source, gen, std, norm_std, device):
+    if any(n < 0 for n in source.shape):
+        raise ValueError(f"{source.name}: a size that only a checkpoint gives ({list(source.shape)}); "
+                         f"the random-weights mode needs it in the configuration")
     if source.init == "zeros":
         return torch.zeros(source.shape, dtype=torch.float32, device=device)
     if source.init == "norm":
