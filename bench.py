@@ -129,6 +129,103 @@ def prefill_flops(cfg, T):
     return linear + attn + 2 * H * V             # logits for the last row only
 
 
+def _latent(heads, dim, rot, vdim, rank, window):
+    return {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+            "rot": {"base": 10000.0, "dims": rot}, "mask": {"size": window}}
+
+
+def _moe(ff, experts, top, groups, keep):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top,
+                                                            "groups": {"count": groups, "keep": keep}}}
+
+
+def design_sizes(design):
+    """name -> (the design's configuration, Llama layers of equal width, depth and active feed-forward weights)."""
+    assert design == "zukotar"
+    out = {}
+    # width, heads, latent rank, experts, top, expert ff, groups, keep | llama heads, kv heads, head size, intermediate
+    for name, W, H, rank, E, top, ff, G, keep, lh, lkv, lhd, inter in (
+            ("w2048", 2048, 16, 512, 16, 6, 2048, 4, 2, 32, 8, 64, 8192),
+            ("w4096", 4096, 32, 512, 32, 8, 2688, 8, 4, 32, 8, 128, 14336)):
+        att = {"type": "latent_attention", "mixer": _latent(H, 128, 64, 128, rank, 4096), "mlp": _moe(ff, E, top, G, keep)}
+        rec = {"type": "gla", "mixer": {"heads": H, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 16},
+               "mlp": _moe(ff, E, top, G, keep)}
+        zk = {"architecture": "Zukotar", "vocab": 32000, "width": W, "embedding": {"scale": W ** 0.5},
+              "norm": {"eps": 1e-6}, "layers": [att, rec, rec, att]}
+        ll = dict(LLAMA_1B, hidden_size=W, num_hidden_layers=4, num_attention_heads=lh, num_key_value_heads=lkv,
+                  head_dim=lhd, intermediate_size=inter, vocab_size=32000)
+        out[name] = (zk, ll)
+    return out
+
+
+def compare_designs(design, W, K):
+    """Prefill (one prompt of 2,048 tokens a step) and decode (8 requests at context 1,024, graph replays) of
+    the design and of Llama layers of equal size: device time per step by CUDA events after W warm-up steps
+    (the median of K), L2 flushed before every timed step, and one step of each kind timed operation by
+    operation (launch by launch, no graphs)."""
+    import torch
+    from rllm_b200.engine import Entry, random_engine
+    pk = peaks()
+    dev = "cuda:0"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    T, B, C = PROMPT, 8, 1024
+    res = {}
+
+    def timed(fn, n):
+        ts = []
+        for i in range(W + n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(i); e1.record()
+            torch.cuda.synchronize()
+            if i >= W:
+                ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    for name, cfgs in design_sizes(design).items():
+        res[name] = {}
+        for arch, cfg in zip((design, "llama"), cfgs):
+            vocab = cfg.get("vocab", cfg.get("vocab_size"))
+            prompt = [(7 * i + 3) % vocab for i in range(T)]
+            r = {}
+            for profiled in (False, True):
+                if profiled:
+                    os.environ["RLLM_B200_PROFILE"] = "1"
+                eng = random_engine(cfg, 0, dtype="bfloat16", device=dev, page_size=PAGE,
+                                    num_pages=(B * (C + 64) + T) // PAGE + 64, max_requests=B + 1)
+                os.environ.pop("RLLM_B200_PROFILE", None)
+
+                def prefill(i):
+                    eng.step([Entry(("p", i), prompt, [T - 1])])
+                    eng.end([("p", i)])
+
+                def decode(i):
+                    eng.step([Entry(("d", b), [(i + b) % vocab], [0]) for b in range(B)])
+
+                if not profiled:
+                    ms = timed(prefill, K)
+                    r["prefill_ms"], r["prefill_tok_s"] = ms, T / ms * 1e3
+                    for b in range(B):
+                        eng.step([Entry(("d", b), prompt[:C], [])])
+                    ms = timed(decode, K)
+                    r["decode_ms"], r["decode_tok_s"], r["decode_graphs"] = ms, B / ms * 1e3, eng.graph_steps
+                else:
+                    prefill(0); eng.backend.report(file=open(os.devnull, "w"))
+                    prefill(1); r["prefill_ops"] = eng.backend.report(file=open(os.devnull, "w"))
+                    for b in range(B):
+                        eng.step([Entry(("d", b), prompt[:C], [])])
+                    decode(0); eng.backend.report(file=open(os.devnull, "w"))
+                    decode(1); r["decode_ops"] = eng.backend.report(file=open(os.devnull, "w"))
+                eng.check()
+                del eng
+                torch.cuda.empty_cache()
+            res[name][arch] = r
+    print(json.dumps({"designs": design, "prompt": T, "decode_batch": B, "decode_context": C, "warmup": W, "steps": K,
+                      "dtype": "bf16", "data": "synthetic, random weights", "l2_flush_between_steps": True,
+                      "peaks": pk, "sizes": res}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -142,6 +239,9 @@ def main():
     ap.add_argument("--workloads", default="", help="comma-separated: mixed_3b, continuous_8b, or all")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (for profiling; the JSON line then lacks the other parts)")
+    ap.add_argument("--designs", default="", choices=["", "zukotar"],
+                    help="instead of the default workload: prefill and decode of this design beside Llama layers of "
+                         "equal size (random weights), with the time per operation; prints its own JSON line")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket one timed step with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     a = ap.parse_args()
@@ -154,6 +254,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     W, K = max(a.warmup, 3), a.steps
+    if a.designs:
+        return compare_designs(a.designs, W, min(K, 16))
 
     import torch
     from rllm_b200.api import LLM

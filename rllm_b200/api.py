@@ -278,8 +278,9 @@ class LLM:
         request then costs what every later one costs."""
         vocab = self.engine.vocab
         limit = getattr(self.engine.model.config, "max_position_embeddings", None) or prompt_len + 8
-        n = max(1, min(prompt_len, self.scheduler.max_tokens_per_step, limit - 8,
-                       (min(self.engine.cache.free_pages()) - 1) * self.engine.cache.page_size - 8))
+        free = self.engine.cache.free_pages()           # empty for a model that keeps state only
+        room = (min(free) - 1) * self.engine.cache.page_size - 8 if free else prompt_len
+        n = max(1, min(prompt_len, self.scheduler.max_tokens_per_step, limit - 8, room))
         prompt = [(7 * i + 1) % vocab for i in range(n)]
         self.generate([prompt], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
         self.generate([prompt[:5]], SamplingParams(temperature=0.8, top_p=0.9, max_tokens=2, ignore_eos=True, seed=0))

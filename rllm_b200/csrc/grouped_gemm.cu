@@ -5,7 +5,7 @@
 //   uniform  every problem g (a head) takes all T rows; its A columns start at g * a_gs, its C columns at
 //            g * c_gs, its weights at B + g * b_gs. grid.z = problems.
 //   ragged   problems (experts) own segments of a sorted row list; a table written on the device by the
-//            routing plan names, per 64-row tile, the problem, the first sorted row and the row count;
+//            routing plan names, per tile of rows, the problem, the first sorted row and the row count;
 //            `rows_in[r]` is the A row a sorted row reads (gather), `rows_out[r]` the C row it writes
 //            (scatter), `row_scale[r]` a float factor. CTAs beyond the table's count leave at once, so the
 //            launch shape depends on the step's size only and never on the routing.
@@ -14,6 +14,14 @@
 //
 // Epilogues: store (storage type), store float, relu(x)^2 (storage type). Optional per-(row, problem)
 // gate g: the result is multiplied by sigmoid(g) (uniform mode).
+//
+// bfloat16 problems whose rows are 16-byte aligned (K, strides and offsets multiples of 8) run on the
+// tensor cores instead (grouped_gemm_mma_kernel): tiles of 128 rows x 128 weight rows x 32 of K, eight warps
+// of 64 x 32 each, `mma.sync` m16n8k16 with float accumulators, operands brought by `cp.async` (gathered rows
+// included) through a ring of three stages and read with `ldmatrix`; a warp leaves out the row tiles of 16
+// that lie beyond the tile's rows, so that a tile with a few rows (decoding) costs its weights' way through
+// the ring and little else. K runs in ascending blocks of 16 inside one accumulator: a row's result is the
+// same wherever it stands. The float path keeps to FMA.
 #include "common.cuh"
 using namespace rllm;
 
@@ -110,6 +118,156 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const GroupedArgs p) 
   }
 }
 
+// ------------------------------------------------------------------------------------------ tensor cores
+constexpr int MB = 128, MN = 128, MK = 32, MSTAGES = 3, MLD = MK + 8;   // 80-byte rows: ldmatrix meets 8 bank groups
+constexpr int MMA_SMEM = MSTAGES * (MB + MN) * MLD * 2;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix4(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const GroupedArgs p) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* As = reinterpret_cast<bf16*>(smem_raw);                      // [MSTAGES][MB][MLD]
+  bf16* Bs = As + MSTAGES * MB * MLD;                                // [MSTAGES][MN][MLD]
+  __shared__ int arow[MB];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 2, wn = warp & 3;                           // 2 x 4 warps, 64 x 32 each
+  int g, row0, rows;
+  if (p.tiles) {
+    if ((int)blockIdx.y >= *p.n_tiles) return;
+    g = p.tiles[3 * blockIdx.y]; row0 = p.tiles[3 * blockIdx.y + 1]; rows = p.tiles[3 * blockIdx.y + 2];
+  } else {
+    g = blockIdx.z; row0 = blockIdx.y * MB; rows = min(MB, p.T - row0);
+  }
+  const int n0 = blockIdx.x * MN;
+  const bf16* A = (const bf16*)p.A + (p.tiles ? 0 : (long long)g * p.a_gs);
+  const bf16* B = (const bf16*)p.B + (long long)g * p.b_gs;
+  if (tid < MB) arow[tid] = tid < rows ? (p.rows_in ? p.rows_in[row0 + tid] : row0 + tid) : -1;
+  __syncthreads();
+
+  // this thread's two 16-byte pieces of each operand per stage: rows tid/4 and tid/4 + 64, 8 of K at (tid%4)*8
+  const int lrow = tid >> 2, lk = (tid & 3) * 8;
+  const long long a0 = arow[lrow] < 0 ? -1 : (long long)arow[lrow] * p.lda;
+  const long long a1 = arow[lrow + 64] < 0 ? -1 : (long long)arow[lrow + 64] * p.lda;
+  const long long b0 = n0 + lrow < p.N ? (long long)(n0 + lrow) * p.K : -1;
+  const long long b1 = n0 + lrow + 64 < p.N ? (long long)(n0 + lrow + 64) * p.K : -1;
+  const int nk = (p.K + MK - 1) / MK;
+  auto load = [&](int kb) {
+    const int st = kb % MSTAGES, k = kb * MK + lk;
+    const int bytes = k < p.K ? 16 : 0;                              // K is a multiple of 8: a piece is whole or empty
+    bf16* as = As + (st * MB + lrow) * MLD + lk;
+    bf16* bs = Bs + (st * MN + lrow) * MLD + lk;
+    cp_async16(as, A + (a0 < 0 || !bytes ? 0 : a0 + k), a0 < 0 ? 0 : bytes);
+    cp_async16(as + 64 * MLD, A + (a1 < 0 || !bytes ? 0 : a1 + k), a1 < 0 ? 0 : bytes);
+    cp_async16(bs, B + (b0 < 0 || !bytes ? 0 : b0 + k), b0 < 0 ? 0 : bytes);
+    cp_async16(bs + 64 * MLD, B + (b1 < 0 || !bytes ? 0 : b1 + k), b1 < 0 ? 0 : bytes);
+  };
+  float acc[4][4][4] = {};
+  // row tiles of 16 this warp has to compute
+  const int mt_live = min(4, max(0, (rows - wm * 64 + 15) / 16));
+#pragma unroll
+  for (int s = 0; s < MSTAGES - 1; ++s) {
+    if (s < nk) load(s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int kb = 0; kb < nk; ++kb) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(MSTAGES - 2) : "memory");
+    __syncthreads();                                                 // block kb has landed; block kb - 1 is used up
+    if (kb + MSTAGES - 1 < nk) load(kb + MSTAGES - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const bf16* as = As + (kb % MSTAGES) * MB * MLD;
+    const bf16* bs = Bs + (kb % MSTAGES) * MN * MLD;
+#pragma unroll
+    for (int kk = 0; kk < MK; kk += 16) {
+      unsigned bfrag[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        ldmatrix4(bfrag[j], bs + (wn * 32 + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * MLD + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (i < mt_live) {
+          unsigned afrag[4];
+          ldmatrix4(afrag, as + (wm * 64 + i * 16 + (lane & 15)) * MLD + kk + (lane >> 4) * 8);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mma16816(acc[i][j], afrag, bfrag[j >> 1][(j & 1) * 2], bfrag[j >> 1][(j & 1) * 2 + 1]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = wm * 64 + i * 16 + (lane >> 2) + half * 8;
+      if (m >= rows) continue;
+      const int r = row0 + m;
+      const long long crow = p.rows_out ? p.rows_out[r] : r;
+      float f = p.row_scale ? p.row_scale[r] : 1.f;
+      if (p.gate) {
+        const float gv = to_f32(((const bf16*)p.gate)[(long long)r * p.gate_ld + g]);
+        f *= 1.f / (1.f + expf(-gv));
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2;
+        if (n >= p.N) continue;
+        float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+        if (EPI == GEPI_RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
+        v0 *= f; v1 *= f;
+        const long long o = crow * p.ldc + (p.tiles ? 0 : (long long)g * p.c_gs) + n;
+        if (EPI == GEPI_STORE_F32) {
+          float* c = (float*)p.C + o;
+          if (n + 1 < p.N && !(o & 1)) *reinterpret_cast<float2*>(c) = make_float2(v0, v1);
+          else { c[0] = v0; if (n + 1 < p.N) c[1] = v1; }
+        } else {
+          bf16* c = (bf16*)p.C + o;
+          if (n + 1 < p.N && !(o & 1)) *reinterpret_cast<__nv_bfloat162*>(c) = __floats2bfloat162_rn(v0, v1);
+          else { c[0] = __float2bfloat16_rn(v0); if (n + 1 < p.N) c[1] = __float2bfloat16_rn(v1); }
+        }
+      }
+    }
+  }
+}
+
+static inline bool mma_ok(const GroupedArgs& p) {
+  return p.K % 8 == 0 && p.lda % 8 == 0 && p.a_gs % 8 == 0 && p.b_gs % 8 == 0 && !((uintptr_t)p.A & 15) &&
+         !((uintptr_t)p.B & 15);
+}
+
+static int launch_mma(int epi, const GroupedArgs& p, dim3 grid, cudaStream_t s) {
+#define GO(E)                                                                                        \
+  do {                                                                                               \
+    static bool done[64] = {};                                                                       \
+    const int rc = allow_dynamic_smem(grouped_gemm_mma_kernel<E>, MMA_SMEM, done);                   \
+    if (rc) return rc;                                                                               \
+    return launch_ex(grouped_gemm_mma_kernel<E>, grid, dim3(256), (size_t)MMA_SMEM, s, 1, p);        \
+  } while (0)
+  switch (epi) {
+    case GEPI_STORE: GO(GEPI_STORE);
+    case GEPI_STORE_F32: GO(GEPI_STORE_F32);
+    case GEPI_RELU2: GO(GEPI_RELU2);
+  }
+#undef GO
+  return ERR_BAD_SIZE;
+}
+
 template <typename TI>
 int launch(int epi, const GroupedArgs& p, dim3 grid, cudaStream_t s) {
   switch (epi) {
@@ -132,21 +290,33 @@ RLLM_API int rllm_grouped_gemm_uniform(int dt, int epi, const void* A, long long
   if ((T + BM - 1) / BM > 65535 || G > 65535) return ERR_TOO_LARGE;
   GroupedArgs p = {A, lda, a_gs, B, b_gs, C, ldc, c_gs, T, N, K, nullptr, nullptr, nullptr, nullptr, nullptr, gate, gate_ld};
   dim3 grid((N + BN - 1) / BN, (T + BM - 1) / BM, G);
+  if (dt == DT_BF16 && mma_ok(p) && (T + MB - 1) / MB <= 65535)
+    return launch_mma(epi, p, dim3((N + MN - 1) / MN, (T + MB - 1) / MB, G), (cudaStream_t)stream);
   if (dt == DT_F32) return launch<float>(epi, p, grid, (cudaStream_t)stream);
   if (dt == DT_BF16) return launch<bf16>(epi, p, grid, (cudaStream_t)stream);
   return ERR_BAD_DTYPE;
 }
 
-// Ragged problems: the tile table (`tiles`, `n_tiles`) comes from rllm_moe_plan; max_tiles bounds the grid.
+// Rows a tile of the plan may have for a problem of this type and shape: the tile of the kernel that will
+// take it (the plan has to be made with it).
+RLLM_API int rllm_grouped_gemm_tile_rows(int dt, long long lda, int K) {
+  return (dt == DT_BF16 && K % 8 == 0 && lda % 8 == 0) ? MB : BM;
+}
+
+// Ragged problems: the tile table (`tiles`, `n_tiles`) comes from rllm_moe_plan, made with tiles of
+// `tile_rows`; max_tiles bounds the grid.
 RLLM_API int rllm_grouped_gemm_ragged(int dt, int epi, const void* A, long long lda, const void* B, long long b_gs,
                                       void* C, long long ldc, int N, int K, const int* tiles, const int* n_tiles,
-                                      int max_tiles, const int* rows_in, const int* rows_out, const float* row_scale,
-                                      void* stream) {
+                                      int max_tiles, int tile_rows, const int* rows_in, const int* rows_out,
+                                      const float* row_scale, void* stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
   if (K <= 0 || !tiles || !n_tiles) return ERR_BAD_SIZE;
   if (max_tiles > 65535) return ERR_TOO_LARGE;
   GroupedArgs p = {A, lda, 0, B, b_gs, C, ldc, 0, 0, N, K, tiles, n_tiles, rows_in, rows_out, row_scale, nullptr, 0};
   dim3 grid((N + BN - 1) / BN, max_tiles, 1);
+  if (dt == DT_BF16 && tile_rows == MB && mma_ok(p))
+    return launch_mma(epi, p, dim3((N + MN - 1) / MN, max_tiles, 1), (cudaStream_t)stream);
+  if (tile_rows != BM) return ERR_BAD_SIZE;                          // the plan was made for the other kernel
   if (dt == DT_F32) return launch<float>(epi, p, grid, (cudaStream_t)stream);
   if (dt == DT_BF16) return launch<bf16>(epi, p, grid, (cudaStream_t)stream);
   return ERR_BAD_DTYPE;

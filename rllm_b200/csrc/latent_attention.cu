@@ -156,6 +156,198 @@ latent_attention_kernel(const TI* __restrict__ qfull, const TI* __restrict__ cac
   }
 }
 
+// ------------------------------------------------------------------------------------------ tensor cores
+// bfloat16, dk a multiple of 8, rank a multiple of 16 up to 512. The rows of the problem are the (token, head)
+// pairs of a sequence's new tokens, 64 to a CTA: since all heads read the same cache rows, the heads of a
+// single decoded token fill a row tile of the tensor core as well as the tokens of a prompt portion do. Keys
+// come 32 at a time through two buffers (`cp.async` through the block table); eight warps = four groups of 16
+// rows x two halves: for the scores each half takes 16 of the 32 keys (QK^T over dk with `mma.sync` m16n8k16,
+// scaled, masked per row by its own position and window, left in shared memory as float), then both halves
+// run the same float softmax update over the 32 scores of their rows and each multiplies the bfloat16 weights
+// with its half of the value columns (the cache row's first `rank` numbers, read with `ldmatrix.trans`).
+// Key tiles begin at the first key that the CTA's first row sees, so where a row's keys fall into tiles, and with it
+// the order of its sums, depends on which rows share its CTA: results differ between cuts of a prompt within
+// bfloat16 rounding (the float path below has one order per position).
+constexpr int QROWS = 64, KT = 32;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix4(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix4t(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+static inline int mma_row_pad(int dk, int nh) {          // numbers per shared-memory row: what ldmatrix may touch, + 8
+  const int a = (dk + 15) / 16 * 16, b = 2 * nh * 8;
+  return (a > b ? a : b) + 8;
+}
+
+template <int NH>     // value columns per half = 8 * NH; rank <= 16 * NH
+__global__ void __launch_bounds__(256, 1)
+latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restrict__ cache, bf16* __restrict__ out,
+                            const int* __restrict__ cu_q, const int* __restrict__ positions,
+                            const int* __restrict__ block_table, int bt_stride, int num_seqs, int H, int rank, int dk,
+                            int ld, int page_size, float scale, int window) {
+  pdl_launch();
+  pdl_wait();
+  // which sequence and which 64 of its (token, head) rows
+  int seq = -1, tile = 0;
+  {
+    int at = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int n = ((cu_q[s + 1] - cu_q[s]) * H + QROWS - 1) / QROWS;
+      if ((int)blockIdx.x < at + n) { seq = s; tile = blockIdx.x - at; break; }
+      at += n;
+    }
+  }
+  if (seq < 0) return;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                      // [64][ld]
+  bf16* ks = qs + QROWS * ld;                                        // [2][32][ld]
+  float* ss = reinterpret_cast<float*>(ks + 2 * KT * ld);            // [64][33]
+  __shared__ int key_ok[2][KT];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = warp >> 1, half = warp & 1;                         // 16 rows each, two halves
+  const int tok0 = cu_q[seq], ntok = cu_q[seq + 1] - tok0;
+  const int row_first = tile * QROWS, nrows = min(QROWS, ntok * H - row_first);
+  const int t_lo = tok0 + row_first / H, t_hi = tok0 + (row_first + nrows - 1) / H;
+  const int pos_lo = positions[t_lo], pos_hi = positions[t_hi];
+  const int key_first = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
+  const int ntiles = (pos_hi - key_first) / KT + 1;
+  const int* bt = block_table + (long long)seq * bt_stride;
+  const int cpr = (ld - 8) / 8;                                      // 16-byte pieces a row is filled with
+
+  auto load_keys = [&](int it) {
+    bf16* dst = ks + (it & 1) * KT * ld;
+    for (int c = tid; c < KT * cpr; c += 256) {
+      const int j = c / cpr, piece = c % cpr;
+      const int kj = key_first + it * KT + j;
+      const int page = kj <= pos_hi ? bt[kj / page_size] : -1;
+      if (piece == 0) key_ok[it & 1][j] = page >= 0;
+      const bool in = page >= 0 && piece * 8 < dk;
+      cp_async16(dst + j * ld + piece * 8,
+                 cache + (in ? ((long long)page * page_size + kj % page_size) * dk + piece * 8 : 0), in ? 16 : 0);
+    }
+  };
+  // the queries, once (rows beyond the sequence's: zeros)
+  for (int c = tid; c < QROWS * cpr; c += 256) {
+    const int r = c / cpr, piece = c % cpr;
+    const bool in = r < nrows && piece * 8 < dk;
+    cp_async16(qs + r * ld + piece * 8, qfull + (in ? ((long long)tok0 * H + row_first + r) * dk + piece * 8 : 0), in ? 16 : 0);
+  }
+  load_keys(0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  // this thread's two rows (of its warp's 16): their positions and first visible keys
+  const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;
+  int pos0 = -1, pos1 = -1, lo0 = 0, lo1 = 0;
+  if (r0 < nrows) { pos0 = positions[tok0 + (row_first + r0) / H]; lo0 = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0; }
+  if (r1 < nrows) { pos1 = positions[tok0 + (row_first + r1) / H]; lo1 = (window > 0 && pos1 - window + 1 > 0) ? pos1 - window + 1 : 0; }
+  const bool rg_live = rg * 16 < nrows;
+  float acc[NH][4];
+#pragma unroll
+  for (int n = 0; n < NH; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int dk16 = (dk + 15) / 16;
+
+  for (int it = 0; it < ntiles; ++it) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                                 // tile `it` has landed; tile it - 1 is used up
+    if (it + 1 < ntiles) load_keys(it + 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const bf16* kt = ks + (it & 1) * KT * ld;
+    const int kbase = key_first + it * KT;
+    if (rg_live) {
+      // scores of this warp's 16 rows against its 16 keys
+      float sc[2][4] = {};
+      for (int kk = 0; kk < dk16; ++kk) {
+        unsigned a[4], b[4];
+        ldmatrix4(a, qs + (rg * 16 + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
+        ldmatrix4(b, kt + (half * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma16816(sc[0], a, b[0], b[1]);
+        mma16816(sc[1], a, b[2], b[3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = half * 16 + j * 8 + (lane & 3) * 2 + (e & 1);
+          const int kj = kbase + col;
+          const bool top = e < 2;
+          const bool seen = key_ok[it & 1][col] && (top ? (kj >= lo0 && kj <= pos0) : (kj >= lo1 && kj <= pos1));
+          ss[(top ? r0 : r1) * (KT + 1) + col] = seen ? sc[j][e] * scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    if (rg_live) {
+      // softmax update of rows r0 and r1 over the tile's 32 scores (this lane holds 8 of each row)
+      float p0[8], p1[8];
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int col = (q >> 1) * 8 + (lane & 3) * 2 + (q & 1);
+        p0[q] = ss[r0 * (KT + 1) + col]; p1[q] = ss[r1 * (KT + 1) + col];
+        mx0 = fmaxf(mx0, p0[q]); mx1 = fmaxf(mx1, p1[q]);
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;     // a row that has seen nothing yet
+      const float c0 = expf(m0 - b0), c1 = expf(m1 - b1);            // m = -inf: 0
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { p0[q] = expf(p0[q] - b0); p1[q] = expf(p1[q] - b1); s0 += p0[q]; s1 += p1[q]; }
+      s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+      l0 = l0 * c0 + s0; l1 = l1 * c1 + s1; m0 = n0; m1 = n1;
+#pragma unroll
+      for (int n = 0; n < NH; ++n) { acc[n][0] *= c0; acc[n][1] *= c0; acc[n][2] *= c1; acc[n][3] *= c1; }
+      // weights as the A operand: keys kk*16 + 2*(lane%4) + {0,1} and + 8
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        unsigned a[4] = {pack_bf16(p0[kk * 4], p0[kk * 4 + 1]), pack_bf16(p1[kk * 4], p1[kk * 4 + 1]),
+                         pack_bf16(p0[kk * 4 + 2], p0[kk * 4 + 3]), pack_bf16(p1[kk * 4 + 2], p1[kk * 4 + 3])};
+#pragma unroll
+        for (int n = 0; n < NH; n += 2) {
+          unsigned b[4];
+          ldmatrix4t(b, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + half * NH * 8 + n * 8 + (lane >> 4) * 8);
+          mma16816(acc[n], a, b[0], b[1]);
+          mma16816(acc[n + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (!rg_live) return;
+  const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+  bf16* o0 = out + ((long long)tok0 * H + row_first + r0) * rank;
+  bf16* o1 = out + ((long long)tok0 * H + row_first + r1) * rank;
+#pragma unroll
+  for (int n = 0; n < NH; ++n) {
+    const int col = half * NH * 8 + n * 8 + (lane & 3) * 2;
+    if (col >= rank) continue;                                       // rank is even: a pair is in or out
+    if (r0 < nrows) *reinterpret_cast<__nv_bfloat162*>(o0 + col) = __floats2bfloat162_rn(acc[n][0] * i0, acc[n][1] * i0);
+    if (r1 < nrows) *reinterpret_cast<__nv_bfloat162*>(o1 + col) = __floats2bfloat162_rn(acc[n][2] * i1, acc[n][3] * i1);
+  }
+}
+
 }  // namespace
 
 // proj [T, ld]: head h's query at q_off + h * (dim + rot) as [dim plain | rot to rotate]; the down-projection
@@ -178,11 +370,36 @@ RLLM_API int rllm_latent_prepare(int dt, const void* proj, long long ld, int q_o
 }
 
 // qfull [T, H, dk]; cache [pages * page_size, dk]; out [T, H, rank].
+// cu_q [num_seqs + 1] (row range of each sequence; null: the tensor-core kernel is not used), `tc` 0 forbids it.
 RLLM_API int rllm_latent_attention(int dt, const void* qfull, const void* cache, void* out, const int* token_seq,
                                    const int* positions, const int* block_table, int bt_stride, int T, int H, int rank,
-                                   int dk, int page_size, float scale, int window, void* stream) {
+                                   int dk, int page_size, float scale, int window, const int* cu_q, int num_seqs,
+                                   int tc, void* stream) {
   if (T <= 0) return 0;
   if (H <= 0 || rank <= 0 || rank > MAX_RANK || dk < rank || page_size <= 0) return ERR_BAD_SIZE;
+  if (tc && dt == DT_BF16 && cu_q && num_seqs > 0 && dk % 8 == 0 && rank % 16 == 0 && rank <= 512 &&
+      !((uintptr_t)qfull & 15) && !((uintptr_t)cache & 15) && !((uintptr_t)out & 3)) {
+    const int nh = rank <= 64 ? 4 : rank <= 128 ? 8 : rank <= 256 ? 16 : 32;
+    const int ld = mma_row_pad(dk, nh);
+    const int smem = (QROWS + 2 * KT) * ld * 2 + QROWS * (KT + 1) * 4;
+    const long long blocks = ((long long)T * H + QROWS - 1) / QROWS + num_seqs;
+    if (smem <= 220 * 1024 && blocks <= 2147483647LL) {
+#define GO(NH)                                                                                                          \
+  do {                                                                                                                  \
+    static bool done[64] = {};                                                                                          \
+    const int rc = allow_dynamic_smem(latent_attention_mma_kernel<NH>, 220 * 1024, done);                               \
+    if (rc) return rc;                                                                                                  \
+    return launch_ex(latent_attention_mma_kernel<NH>, dim3((unsigned)blocks), dim3(256), (size_t)smem,                  \
+                     (cudaStream_t)stream, 1, (const bf16*)qfull, (const bf16*)cache, (bf16*)out, cu_q, positions,      \
+                     block_table, bt_stride, num_seqs, H, rank, dk, ld, page_size, scale, window);                      \
+  } while (0)
+      if (nh == 4) GO(4);
+      if (nh == 8) GO(8);
+      if (nh == 16) GO(16);
+      GO(32);
+#undef GO
+    }
+  }
   const int hg = H < HG ? H : HG;
   const int smem = (32 * (dk | 1) + hg * dk) * (int)sizeof(float);
   if (smem > 200 * 1024) return ERR_TOO_LARGE;

@@ -6,7 +6,7 @@
 //   are the scores themselves, or the scores divided by their sum (`renorm`). All in float. Of equal
 //   scores the lower index wins.
 // moe_plan: from the choices, the sorted row list the grouped product walks: per expert a segment of
-//   (token, slot) pairs, cut into tiles of 64 rows. One CTA; a pair's place inside its expert's segment is
+//   (token, slot) pairs, cut into tiles of `tile_rows` rows. One CTA; a pair's place inside its expert's segment is
 //   handed out by a counter, which changes where a row is computed, never its value.
 // rmsnorm_add: residual[t] += w * y[t] / sqrt(mean(y[t]^2) + eps) with y[t] = sum over `parts` of
 //   parts_in[t, p, :] in order (parts = 1: a plain post-norm; more: the combine of the chosen experts'
@@ -17,7 +17,6 @@ using namespace rllm;
 namespace {
 
 constexpr int MAX_E = 1024;      // experts a warp can rank (32 per lane)
-constexpr int TILE_ROWS = 64;    // rows of a tile of the grouped product
 
 __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int groups,
                                                        int keep, int top, int renorm, int* __restrict__ idx,
@@ -85,7 +84,7 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
 
 // counts -> segments -> tiles -> places. n = T * top pairs, pair i = token i / top, slot i % top.
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ idx, const float* __restrict__ wt, int n,
-                                                        int top, int E, int* __restrict__ rows_tok,
+                                                        int top, int E, int tile_rows, int* __restrict__ rows_tok,
                                                         int* __restrict__ rows_dest, float* __restrict__ rows_scale,
                                                         int* __restrict__ tiles, int* __restrict__ n_tiles) {
   pdl_launch();
@@ -99,8 +98,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
     int at = 0, nt = 0;
     for (int e = 0; e < E; ++e) {
       cursor[e] = at;
-      for (int r = 0; r < count[e]; r += TILE_ROWS) {
-        tiles[3 * nt] = e; tiles[3 * nt + 1] = at + r; tiles[3 * nt + 2] = min(TILE_ROWS, count[e] - r);
+      for (int r = 0; r < count[e]; r += tile_rows) {
+        tiles[3 * nt] = e; tiles[3 * nt + 1] = at + r; tiles[3 * nt + 2] = min(tile_rows, count[e] - r);
         ++nt;
       }
       at += count[e];
@@ -155,14 +154,14 @@ RLLM_API int rllm_moe_topk(const float* logits, int T, int E, int groups, int ke
                    keep, top, renorm, idx, wt);
 }
 
-// tiles: room for n / 64 + E entries of 3 ints.
-RLLM_API int rllm_moe_plan(const int* idx, const float* wt, int T, int top, int E, int* rows_tok, int* rows_dest,
-                           float* rows_scale, int* tiles, int* n_tiles, void* stream) {
+// tiles: room for n / tile_rows + E entries of 3 ints.
+RLLM_API int rllm_moe_plan(const int* idx, const float* wt, int T, int top, int E, int tile_rows, int* rows_tok,
+                           int* rows_dest, float* rows_scale, int* tiles, int* n_tiles, void* stream) {
   if (T <= 0) return 0;
-  if (E <= 0 || E > MAX_E || top <= 0) return ERR_BAD_SIZE;
+  if (E <= 0 || E > MAX_E || top <= 0 || tile_rows <= 0) return ERR_BAD_SIZE;
   if ((long long)T * top > 2147483647LL) return ERR_TOO_LARGE;
-  return launch_ex(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, 1, idx, wt, T * top, top, E, rows_tok,
-                   rows_dest, rows_scale, tiles, n_tiles);
+  return launch_ex(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, 1, idx, wt, T * top, top, E, tile_rows,
+                   rows_tok, rows_dest, rows_scale, tiles, n_tiles);
 }
 
 RLLM_API int rllm_rmsnorm_add(const float* y, int parts, const float* w, float* residual, int T, int H, float eps,

@@ -71,7 +71,7 @@ class Backend:
         of K to merge) takes no norm in front (64 tokens: 14.8 us + the norm's 2 against 19.4)."""
         if gate_up and isinstance(x, Normed) and x.shape[0] > 32:
             return False
-        if not (isinstance(x, Normed) and x._tensor is None and self._sm100 is not None
+        if not (isinstance(x, Normed) and x._tensor is None and self._sm100 is not None and w.shape[0] % 4 == 0
                 and os.environ.get("RLLM_B200_NO_NORM_FUSION") != "1"
                 and self._sm100.norm_supported(x.h, x.weight, w, x.rows)):
             return False
@@ -196,10 +196,15 @@ class Backend:
         return self._mix.grouped_gemm_uniform(a, a_gs, w, out, c_gs,
                                               self._mix.GEPI_STORE_F32 if f32 else self._mix.GEPI_STORE, gate=gate)
 
-    def route(self, logits, top, groups=1, keep=1, renorm=False):
+    def expert_tile_rows(self, x, w_up, w_down):
+        """Rows per tile of a plan that the up and the down product of a routed feed-forward share."""
+        return min(self._mix.tile_rows(x.dtype, x.stride(0), w_up.shape[2]),
+                   self._mix.tile_rows(x.dtype, w_down.shape[2], w_down.shape[2]))
+
+    def route(self, logits, top, groups=1, keep=1, renorm=False, tile_rows=64):
         """Router logits -> the plan of the experts' grouped products (all on the device)."""
         idx, wt = self._mix.moe_topk(logits, top, groups, keep, renorm)
-        return idx, wt, self._mix.moe_plan(idx, wt, logits.shape[1])
+        return idx, wt, self._mix.moe_plan(idx, wt, logits.shape[1], tile_rows)
 
     def experts_up(self, x, w_up, plan, act="relu2"):
         """act(x[token of row] W_up[expert of row]^T) for every sorted row of the plan."""
@@ -220,7 +225,8 @@ class Backend:
 
     def latent_attention(self, qfull, cache, ctx, rank, scale, window):
         return self._mix.latent_attention(qfull, cache.tensors["kv"], ctx.token_seq, ctx.positions,
-                                          cache.block_table, rank, scale, window)
+                                          cache.block_table, rank, scale, window, cu_q=ctx.cu_q, num_seqs=ctx.num_seqs,
+                                          tensor_cores=self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1")
 
     def gla_scan(self, *a, **k):
         return self._mix.gla_scan(*a, **k)

@@ -16,20 +16,21 @@ from .ops import KernelError, _check, _cuda, _dt, _fn, _ptr, _stream
 
 _P, _LL = ops._P, c_longlong
 GEPI_STORE, GEPI_STORE_F32, GEPI_RELU2 = 0, 1, 2
-TILE_ROWS = 64
 
 ops.register_signatures("mix", {
     "rllm_grouped_gemm_uniform": [c_int, c_int, _P, _LL, _LL, _P, _LL, _P, _LL, _LL, c_int, c_int, c_int, c_int,
                                   _P, _LL, _P],
-    "rllm_grouped_gemm_ragged": [c_int, c_int, _P, _LL, _P, _LL, _P, _LL, c_int, c_int, _P, _P, c_int, _P, _P, _P, _P],
+    "rllm_grouped_gemm_ragged": [c_int, c_int, _P, _LL, _P, _LL, _P, _LL, c_int, c_int, _P, _P, c_int, c_int, _P, _P, _P,
+                                 _P],
+    "rllm_grouped_gemm_tile_rows": [c_int, _LL, c_int],
     "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
-    "rllm_moe_plan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
+    "rllm_moe_plan": [_P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "rllm_rmsnorm_add": [_P, c_int, _P, _P, c_int, c_int, c_float, _P],
     "rllm_add_row": [_P, _P, c_int, c_int, _P],
     "rllm_latent_prepare": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_float, _P,
                             _P, _P, _P, _P],
     "rllm_latent_attention": [c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                              c_int, _P],
+                              c_int, _P, c_int, c_int, _P],
     "rllm_gla_scan": [c_int, _P, _LL, c_int, c_int, c_int, _P, _P, c_float, c_float, c_int, c_int, c_int, c_int,
                       _P, _P, _P, _P, _P],
     "rllm_gla_finish": [c_int, _P, _P, c_float, _P, _LL, c_int, c_int, c_int, c_int, _P, _P],
@@ -109,7 +110,14 @@ class RoutePlan:
     """What `moe_plan` leaves on the device for the grouped products of one routed feed-forward: per
     sorted row the token it reads (`rows_tok`), the (token, slot) row it writes (`rows_dest`) and its
     weight (`rows_scale`); the tile table and its length."""
-    __slots__ = ("rows_tok", "rows_dest", "rows_scale", "tiles", "n_tiles", "max_tiles", "n_rows")
+    __slots__ = ("rows_tok", "rows_dest", "rows_scale", "tiles", "n_tiles", "max_tiles", "n_rows", "tile_rows")
+
+
+def tile_rows(dtype: torch.dtype, lda: int, K: int) -> int:
+    """Rows a plan's tile may have for a ragged product whose input has dtype `dtype`, row stride `lda` and
+    depth K: 128 where the tensor-core kernel takes it, 64 for the CUDA-core one. The products that share a
+    plan must agree (take the smallest)."""
+    return _fn("mix", "rllm_grouped_gemm_tile_rows")(ops._DT[dtype], int(lda), int(K))
 
 
 def moe_topk(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
@@ -124,20 +132,20 @@ def moe_topk(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
     return idx, wt
 
 
-def moe_plan(idx: torch.Tensor, wt: torch.Tensor, experts: int) -> RoutePlan:
+def moe_plan(idx: torch.Tensor, wt: torch.Tensor, experts: int, rows_per_tile: int = 64) -> RoutePlan:
     _i32(idx, "idx")
     _f32(wt, "wt", idx.shape)
     T, top = idx.shape
     n, dev = T * top, idx.device
     p = RoutePlan()
-    p.n_rows = n
-    p.max_tiles = n // TILE_ROWS + experts
+    p.n_rows, p.tile_rows = n, int(rows_per_tile)
+    p.max_tiles = n // p.tile_rows + experts
     p.rows_tok = torch.empty(n, dtype=torch.int32, device=dev)
     p.rows_dest = torch.empty(n, dtype=torch.int32, device=dev)
     p.rows_scale = torch.empty(n, dtype=torch.float32, device=dev)
     p.tiles = torch.empty(3 * p.max_tiles, dtype=torch.int32, device=dev)
     p.n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
-    _check(_fn("mix", "rllm_moe_plan")(idx.data_ptr(), wt.data_ptr(), T, top, experts, p.rows_tok.data_ptr(),
+    _check(_fn("mix", "rllm_moe_plan")(idx.data_ptr(), wt.data_ptr(), T, top, experts, p.tile_rows, p.rows_tok.data_ptr(),
                                        p.rows_dest.data_ptr(), p.rows_scale.data_ptr(), p.tiles.data_ptr(),
                                        p.n_tiles.data_ptr(), _stream()), "moe_plan")
     return p
@@ -160,7 +168,8 @@ def grouped_gemm_ragged(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: 
         raise KernelError("grouped product: a has fewer rows than the plan")
     _check(_fn("mix", "rllm_grouped_gemm_ragged")(
         _dt(a, "a"), epilogue, a.data_ptr(), a.stride(0), w.data_ptr(), N * K, out.data_ptr(), out.stride(0), N, K,
-        plan.tiles.data_ptr(), plan.n_tiles.data_ptr(), plan.max_tiles, plan.rows_tok.data_ptr() if gather else None,
+        plan.tiles.data_ptr(), plan.n_tiles.data_ptr(), plan.max_tiles, plan.tile_rows,
+        plan.rows_tok.data_ptr() if gather else None,
         plan.rows_dest.data_ptr() if scatter else None, plan.rows_scale.data_ptr() if scale else None, _stream()),
         "grouped_gemm_ragged")
     return out
@@ -192,8 +201,11 @@ def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: int, heads: int, dim
 
 
 def latent_attention(qfull: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
-                     block_table: torch.Tensor, rank: int, scale: float, window: int | None) -> torch.Tensor:
-    """qfull [T, heads, dk]; cache [pages, page, dk] -> [T, heads, rank] of qfull's dtype."""
+                     block_table: torch.Tensor, rank: int, scale: float, window: int | None,
+                     cu_q: torch.Tensor | None = None, num_seqs: int = 0, tensor_cores: bool = True) -> torch.Tensor:
+    """qfull [T, heads, dk]; cache [pages, page, dk] -> [T, heads, rank] of qfull's dtype. With `cu_q`
+    (int32 [num_seqs + 1], the row range of each sequence) bfloat16 problems of fitting sizes run on the
+    tensor cores (`tensor_cores` False: never)."""
     _cuda(qfull, "qfull"); _cuda(cache, "cache")
     T, H, dk = qfull.shape
     if not qfull.is_contiguous() or not cache.is_contiguous() or cache.dtype != qfull.dtype or cache.dim() != 3 \
@@ -203,11 +215,14 @@ def latent_attention(qfull: torch.Tensor, cache: torch.Tensor, token_seq: torch.
         _i32(t, n, T)
     if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.stride(1) != 1:
         raise KernelError("block_table must be int32 [sequences, pages] with unit inner stride")
+    if cu_q is not None:
+        _i32(cu_q, "cu_q", num_seqs + 1)
     out = torch.empty((T, H, rank), dtype=qfull.dtype, device=qfull.device)
     _check(_fn("mix", "rllm_latent_attention")(
         _dt(qfull, "qfull"), qfull.data_ptr(), cache.data_ptr(), out.data_ptr(), token_seq.data_ptr(),
         positions.data_ptr(), block_table.data_ptr(), block_table.stride(0), T, H, rank, dk, cache.shape[1],
-        float(scale), int(window or 0), _stream()), "latent_attention")
+        float(scale), int(window or 0), _ptr(cu_q), int(num_seqs), int(bool(tensor_cores)), _stream()),
+        "latent_attention")
     return out
 
 

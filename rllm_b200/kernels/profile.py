@@ -143,6 +143,55 @@ class OpProfile:
         nbytes = sum(seen) * nkv * hd * 2 * cache.k.element_size() + 2 * _nbytes(q)
         return self._timed("attention", nbytes, 4 * nh * hd * pairs, self._be.attention, q, cache, ctx, nh, scale, window)
 
+    # ---- mixers with latents or a recurrent state, routed feed-forwards
+    def rmsnorm_add(self, residual, y, w, eps):
+        return self._timed("norm+add", _nbytes(y) + 2 * _nbytes(residual), 0, self._be.rmsnorm_add, residual, y, w, eps)
+
+    def linear_heads(self, a, a_gs, w, out, c_gs, f32=False, gate=None):
+        T, (G, N, K) = a.shape[0], w.shape
+        return self._timed("heads", _nbytes(w) + T * G * (N + K) * a.element_size(), 2 * T * G * N * K,
+                           self._be.linear_heads, a, a_gs, w, out, c_gs, f32=f32, gate=gate)
+
+    def expert_tile_rows(self, *a):
+        return self._be.expert_tile_rows(*a)
+
+    def route(self, logits, *a, **k):
+        return self._timed("route", 2 * _nbytes(logits), 0, self._be.route, logits, *a, **k)
+
+    def experts_up(self, x, w_up, plan, act="relu2"):
+        E, F, W = w_up.shape
+        return self._timed("experts_up", _nbytes(w_up) + plan.n_rows * (F + W) * x.element_size(), 2 * plan.n_rows * F * W,
+                           self._be.experts_up, x, w_up, plan, act)
+
+    def experts_down(self, a, w_down, plan, T, top):
+        E, W, F = w_down.shape
+        return self._timed("experts_down", _nbytes(w_down) + plan.n_rows * (F * a.element_size() + 4 * W),
+                           2 * plan.n_rows * F * W, self._be.experts_down, a, w_down, plan, T, top)
+
+    def latent_prepare(self, proj, *a, **k):
+        return self._timed("latent_prepare", 2 * _nbytes(proj), 0, self._be.latent_prepare, proj, *a, **k)
+
+    def latent_attention(self, qfull, cache, ctx, rank, scale, window):
+        T, H, dk = qfull.shape
+        lens, qs = ctx.kv_lens_host, ctx.q_lens_host
+        if lens is None:
+            lens, qs = [ctx.max_kv_len] * ctx.num_seqs, [1] * ctx.num_seqs
+        seen = [min(L, window + q - 1) if window else L for L, q in zip(lens, qs)]
+        pairs = sum(q * (s - q) + q * (q + 1) // 2 for s, q in zip(seen, qs))
+        nbytes = sum(seen) * dk * qfull.element_size() + _nbytes(qfull) + T * H * rank * qfull.element_size()
+        return self._timed("latent_attention", nbytes, 2 * H * (dk + rank) * pairs, self._be.latent_attention,
+                           qfull, cache, ctx, rank, scale, window)
+
+    def gla_scan(self, proj, q_off, k_off, v_off, z, zbias, tau, qscale, heads, dim, vdim, cu_q, num_seqs, slots, state):
+        T = proj.shape[0]
+        nbytes = T * heads * (2 * dim + vdim) * proj.element_size() + _nbytes(z) + T * heads * vdim * 4 \
+            + 2 * num_seqs * heads * dim * vdim * 4
+        return self._timed("gla_scan", nbytes, 5 * T * heads * dim * vdim, self._be.gla_scan, proj, q_off, k_off, v_off, z,
+                           zbias, tau, qscale, heads, dim, vdim, cu_q, num_seqs, slots, state)
+
+    def gla_finish(self, o, *a, **k):
+        return self._timed("gla_finish", 2 * _nbytes(o), 0, self._be.gla_finish, o, *a, **k)
+
     def argmax(self, logits):
         return self._timed("sample", _nbytes(logits), 0, self._be.argmax, logits)
 

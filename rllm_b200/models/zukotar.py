@@ -58,7 +58,10 @@ def build_zukotar(cfg: ZukotarConfig) -> Model:
     final_norm.prefix = "final."
     head = make_part("head", "linear", vocab=cfg.vocab, hidden=W, norm=final_norm, tied_to=emb)
     head.prefix = ""
-    return Model(cfg, emb, blocks, schedule, head, prefix="")
+    model = Model(cfg, emb, blocks, schedule, head, prefix="")
+    # a layer without feed-forward has no use for the norms around one, should a checkpoint carry them
+    model.ignorable = tuple(f"l{i}.norm2{b}" for i, layer in enumerate(cfg.layers) if layer.mlp is None for b in ("", "b"))
+    return model
 
 
 register_architecture("Zukotar", ZukotarConfig, build_zukotar, model_types=("zukotar",))

@@ -40,7 +40,8 @@ class RoutedExperts(Part):
             raise NotImplementedError("RoutedExperts returns its parts; the block sums them")
         be = ctx.backend
         x = x.tensor() if hasattr(x, "tensor") else x
-        _, _, plan = be.route(be.linear_f32(x, self.w_router), self.top, self.groups, self.keep, self.renorm)
+        _, _, plan = be.route(be.linear_f32(x, self.w_router), self.top, self.groups, self.keep, self.renorm,
+                              tile_rows=be.expert_tile_rows(x, self._up, self._down))
         return be.experts_down(be.experts_up(x, self._up, plan, self.act), self._down, plan, x.shape[0], self.top)
 
 

@@ -70,8 +70,9 @@ def load_weights(model, model_dir: str, dtype: torch.dtype, device) -> None:
         exp = expected_tensors(model)
         names = {n for n, *_ in exp}
         missing = sorted(n for n in names if n not in store.entries)
+        ignorable = IGNORABLE + tuple(getattr(model, "ignorable", ()))     # a model may name tensors it has no use for
         unexpected = sorted(n for n in store.names() if n not in names
-                            and not any(fnmatch.fnmatch(n, pat) for pat in IGNORABLE))
+                            and not any(fnmatch.fnmatch(n, pat) for pat in ignorable))
         wrong_shape, wrong_dtype = [], []
         for n, s, p, _ in exp:
             ent = store.entries.get(n)

@@ -51,8 +51,17 @@ ZC = {  # the loop covers the last layers; wide recurrent heads; sizes that are 
     ],
     "loop": {"start": 1, "stop": 2, "times": 2},
 }
+ZD = {  # recurrent layers only (no pages at all), all of them looped, one without feed-forward
+    "architecture": "Zukotar", "vocab": 90, "width": 40, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "gla", "mixer": {"heads": 2, "dim": 12, "vdim": 20, "tau": 8.0, "decay_rank": 4}, "mlp": None},
+        {"type": "gla", "mixer": {"heads": 5, "dim": 8, "vdim": 8, "tau": 1.0, "decay_rank": 12}, "mlp": moe(16, 3, 3)},
+    ],
+    "loop": {"start": 0, "stop": 2, "times": 2},
+}
 # name -> (config, seed, weight std, norm std, page size)
-TINY = {"ZA": (ZA, 11, 0.09, 0.2, 4), "ZB": (ZB, 12, 0.12, 0.1, 8), "ZC": (ZC, 13, 0.1, 0.3, 16)}
+TINY = {"ZA": (ZA, 11, 0.09, 0.2, 4), "ZB": (ZB, 12, 0.12, 0.1, 8), "ZC": (ZC, 13, 0.1, 0.3, 16),
+        "ZD": (ZD, 14, 0.15, 0.2, 16)}
 
 
 def make_model_dir(root, name, dtype=torch.bfloat16):
