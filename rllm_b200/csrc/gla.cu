@@ -1,16 +1,23 @@
 // Gated linear attention as a recurrence over a per-request state, float arithmetic throughout.
 //
 // Per head, with key channels k < dim and value columns v < vdim:
-//   alpha_t[k] = sigmoid(z_t[k] + b[k]) ^ (1 / tau)          computed as exp(logsigmoid(.) / tau)
+//   alpha_t[k] = sigmoid(z_t[k] + b[k]) ^ (1 / tau)          computed as exp(logsigmoid(.) / tau)   (gla_decay)
 //   S_t[k, v]  = alpha_t[k] * S_(t-1)[k, v] + key_t[k] * value_t[v]
 //   o_t[v]     = sum_k S_t[k, v] * (query_t[k] * qscale)
 // The state S lives in float in a slot per request and is carried from step to step; a step brings any
-// number of tokens of a sequence (a prompt portion or one decoded token): the same kernel, the same order
-// of every sum, so the result does not depend on how the tokens were cut into steps.
+// number of tokens of a sequence (a prompt portion or one decoded token).
 //
-// gla_scan: one CTA per (sequence, head, 32 value columns); the four warps split the key channels, a lane
-//   owns a value column and keeps its share of S in registers while it walks the sequence's tokens, eight
-//   at a time through shared memory. The four warps' partial sums of o are added in warp order.
+// gla_scan (mode WHOLE): one CTA per (sequence, head, 32 value columns); the four warps split the key
+//   channels, a lane owns a value column and keeps its share of S in registers while it walks the sequence's
+//   tokens, eight at a time through shared memory. The four warps' partial sums of o are added in warp order.
+//   A position's result is the same bits whether its tokens came one by one or in portions.
+// Long portions (the caller decides by the longest portion of the step) are cut into chunks of `chunk` tokens
+//   that run side by side, which the recurrence allows because it is linear in S: with A_c the product of
+//   a chunk's alphas and B_c the state the chunk builds from zero, S_end = diag(A_c) S_start + B_c.
+//   Pass LOCAL computes A_c and B_c per chunk, gla_carry walks the chunks of a sequence once
+//   (S_start of each chunk, the final state into the slot), pass FINAL runs each chunk again from its
+//   S_start and writes the outputs. Twice the arithmetic, chunks-fold the parallelism; sums are grouped
+//   differently than token by token, within float rounding.
 // gla_finish: one warp per (token, head): o / sqrt(mean(o^2) + eps) * w over vdim, times silu(gate).
 #include "common.cuh"
 using namespace rllm;
@@ -19,77 +26,137 @@ namespace {
 
 constexpr int CH = 8;            // tokens staged at a time
 constexpr int MAX_DIM = 256;     // key channels per head
+enum : int { WHOLE = 0, LOCAL = 1, FINAL = 2 };
 
-template <typename TI, int KP>   // KP: state registers a thread, 4 * KP >= dim
+__global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict__ bias, int n, long long total,
+                                 float inv_tau) {
+  pdl_launch();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const float zz = z[i] + bias[i % n];
+    const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));      // ln sigmoid(zz)
+    z[i] = expf(ls * inv_tau);
+  }
+}
+
+// Which sequence and which of its chunks a CTA of a chunked pass has; false: none.
+__device__ __forceinline__ bool find_chunk(const int* cu_q, int num_seqs, int chunk, int b, int& seq, int& c, int& base) {
+  int at = 0;
+  for (int s = 0; s < num_seqs; ++s) {
+    const int n = (cu_q[s + 1] - cu_q[s] + chunk - 1) / chunk;
+    if (b < at + n) { seq = s; c = b - at; base = at; return true; }
+    at += n;
+  }
+  return false;
+}
+
+template <typename TI, int KP, int MODE>   // KP: state registers a thread, 4 * KP >= dim
 __global__ void __launch_bounds__(128)
-gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, const float* __restrict__ z,
-                const float* __restrict__ zbias, float inv_tau, float qscale, int H, int dim, int vdim,
-                const int* __restrict__ cu_q, const int* __restrict__ state_slots, float* __restrict__ state,
-                float* __restrict__ out) {
+gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
+                const float* __restrict__ alpha, float qscale, int H, int dim, int vdim,
+                const int* __restrict__ cu_q, int num_seqs, const int* __restrict__ state_slots,
+                float* __restrict__ state, float* __restrict__ out, int chunk, float* __restrict__ chunk_state,
+                float* __restrict__ chunk_decay) {
   pdl_launch();
   pdl_wait();
   __shared__ float qs[CH][MAX_DIM], ks[CH][MAX_DIM], as[CH][MAX_DIM];
   __shared__ float vs[CH][32];
   __shared__ float part[CH][4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.x, h = blockIdx.y, v = blockIdx.z * 32 + lane;
-  const int row0 = cu_q[seq], row1 = cu_q[seq + 1];
-  const int slot = state_slots ? state_slots[seq] : -1;
+  const int h = blockIdx.y, v = blockIdx.z * 32 + lane;
+  int seq = blockIdx.x, c = 0, base = 0;
+  if (MODE != WHOLE && !find_chunk(cu_q, num_seqs, chunk, blockIdx.x, seq, c, base)) return;
+  int row0 = cu_q[seq], row1 = cu_q[seq + 1];
+  if (MODE != WHOLE) { row0 += c * chunk; row1 = min(row1, row0 + chunk); }
+  const int slot = (MODE == WHOLE && state_slots) ? state_slots[seq] : -1;
   const int kp = (dim + 3) / 4;                  // key channels of a warp
   const int kbase = warp * kp;
   const bool vok = v < vdim;
-  float S[KP];
-  float* sp = state + (((long long)(slot < 0 ? 0 : slot) * H + h) * dim) * vdim + v;
+  float S[KP], A[MODE == LOCAL ? KP : 1];
+  // where this thread's share of a state lies: the request's slot, or the chunk's place in the scratch
+  float* sp = (MODE == WHOLE ? state + ((long long)(slot < 0 ? 0 : slot) * H + h) * dim * vdim
+                             : chunk_state + ((long long)(base + c) * H + h) * dim * vdim) + v;
 #pragma unroll
   for (int i = 0; i < KP; ++i) {
     const int k = kbase + i;
-    S[i] = (slot >= 0 && vok && i < kp && k < dim) ? sp[(long long)k * vdim] : 0.f;
+    const bool mine = vok && i < kp && k < dim;
+    S[i] = ((MODE == WHOLE ? slot >= 0 : MODE == FINAL) && mine) ? sp[(long long)k * vdim] : 0.f;
+    if (MODE == LOCAL) A[i] = 1.f;
   }
   for (int c0 = row0; c0 < row1; c0 += CH) {
     const int n = min(CH, row1 - c0);
     for (int x = threadIdx.x; x < n * dim; x += 128) {
-      const int c = x / dim, k = x % dim;
-      const TI* r = proj + (long long)(c0 + c) * ld;
-      qs[c][k] = to_f32(r[q_off + h * dim + k]) * qscale;
-      ks[c][k] = to_f32(r[k_off + h * dim + k]);
-      const float zz = z[(long long)(c0 + c) * H * dim + h * dim + k] + zbias[h * dim + k];
-      const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));      // ln sigmoid(zz)
-      as[c][k] = expf(ls * inv_tau);
+      const int cc = x / dim, k = x % dim;
+      const TI* r = proj + (long long)(c0 + cc) * ld;
+      qs[cc][k] = to_f32(r[q_off + h * dim + k]) * qscale;
+      ks[cc][k] = to_f32(r[k_off + h * dim + k]);
+      as[cc][k] = alpha[(long long)(c0 + cc) * H * dim + h * dim + k];
     }
     for (int x = threadIdx.x; x < n * 32; x += 128) {
-      const int c = x >> 5, j = x & 31;
+      const int cc = x >> 5, j = x & 31;
       const int vv = blockIdx.z * 32 + j;
-      vs[c][j] = vv < vdim ? to_f32(proj[(long long)(c0 + c) * ld + v_off + h * vdim + vv]) : 0.f;
+      vs[cc][j] = vv < vdim ? to_f32(proj[(long long)(c0 + cc) * ld + v_off + h * vdim + vv]) : 0.f;
     }
     __syncthreads();
-    for (int c = 0; c < n; ++c) {
-      const float val = vs[c][lane];
+    for (int cc = 0; cc < n; ++cc) {
+      const float val = vs[cc][lane];
       float o = 0.f;
 #pragma unroll
       for (int i = 0; i < KP; ++i) {
         const int k = kbase + i;
         if (i < kp && k < dim) {
-          S[i] = fmaf(as[c][k], S[i], ks[c][k] * val);
-          o = fmaf(S[i], qs[c][k], o);
+          S[i] = fmaf(as[cc][k], S[i], ks[cc][k] * val);
+          if (MODE == LOCAL) A[i] *= as[cc][k];
+          else o = fmaf(S[i], qs[cc][k], o);
         }
       }
-      part[c][warp][lane] = o;
+      if (MODE != LOCAL) part[cc][warp][lane] = o;
     }
     __syncthreads();
-    for (int x = threadIdx.x; x < n * 32; x += 128) {
-      const int c = x >> 5, j = x & 31;
-      const int vv = blockIdx.z * 32 + j;
-      if (vv < vdim)
-        out[((long long)(c0 + c) * H + h) * vdim + vv] = ((part[c][0][j] + part[c][1][j]) + part[c][2][j]) + part[c][3][j];
-    }
+    if (MODE != LOCAL)
+      for (int x = threadIdx.x; x < n * 32; x += 128) {
+        const int cc = x >> 5, j = x & 31;
+        const int vv = blockIdx.z * 32 + j;
+        if (vv < vdim)
+          out[((long long)(c0 + cc) * H + h) * vdim + vv] = ((part[cc][0][j] + part[cc][1][j]) + part[cc][2][j]) + part[cc][3][j];
+      }
   }
-  if (slot >= 0 && vok) {
+  if (MODE != FINAL && vok && !(MODE == WHOLE && slot < 0)) {
 #pragma unroll
     for (int i = 0; i < KP; ++i) {
       const int k = kbase + i;
-      if (i < kp && k < dim) sp[(long long)k * vdim] = S[i];
+      if (i < kp && k < dim) {
+        sp[(long long)k * vdim] = S[i];
+        if (MODE == LOCAL && blockIdx.z == 0 && lane == 0) chunk_decay[((long long)(base + c) * H + h) * dim + k] = A[i];
+      }
     }
   }
+}
+
+// One thread per state element of a (sequence, head): S walks the sequence's chunks; chunk_state[c] turns from
+// B_c into the state the chunk starts from, and the slot gets the state after the last chunk.
+__global__ void gla_carry_kernel(const int* __restrict__ cu_q, const int* __restrict__ state_slots,
+                                 float* __restrict__ state, float* __restrict__ chunk_state,
+                                 const float* __restrict__ chunk_decay, int chunk, int H, int dim, int vdim) {
+  pdl_launch();
+  pdl_wait();
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  if (e >= dim * vdim) return;
+  int base = 0;
+  for (int s = 0; s < seq; ++s) base += (cu_q[s + 1] - cu_q[s] + chunk - 1) / chunk;
+  const int n = (cu_q[seq + 1] - cu_q[seq] + chunk - 1) / chunk;
+  const int slot = state_slots ? state_slots[seq] : -1;
+  float* sp = state + ((long long)(slot < 0 ? 0 : slot) * H + h) * dim * vdim + e;
+  float S = slot >= 0 ? *sp : 0.f;
+  const int k = e / vdim;
+  for (int c = 0; c < n; ++c) {
+    float* b = chunk_state + ((long long)(base + c) * H + h) * dim * vdim + e;
+    const float next = fmaf(chunk_decay[((long long)(base + c) * H + h) * dim + k], S, *b);
+    *b = S;
+    S = next;
+  }
+  if (slot >= 0) *sp = S;
 }
 
 template <typename TI>
@@ -115,35 +182,63 @@ gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ w, floa
   }
 }
 
+template <typename TI, int MODE>
+int scan(dim3 grid, cudaStream_t s, const void* proj, long long ld, int q_off, int k_off, int v_off, const float* alpha,
+         float qscale, int H, int dim, int vdim, const int* cu_q, int num_seqs, const int* state_slots, float* state,
+         float* out, int chunk, float* chunk_state, float* chunk_decay) {
+  const int kp = (dim + 3) / 4;
+#define GO(KP)                                                                                                        \
+  return launch_ex(gla_scan_kernel<TI, KP, MODE>, grid, dim3(128), 0, s, 1, (const TI*)proj, ld, q_off, k_off, v_off, \
+                   alpha, qscale, H, dim, vdim, cu_q, num_seqs, state_slots, state, out, chunk, chunk_state, chunk_decay)
+  if (kp <= 8) GO(8);
+  if (kp <= 16) GO(16);
+  if (kp <= 32) GO(32);
+  GO(64);
+#undef GO
+}
+
 }  // namespace
 
+// z float [T, n] (n = H * dim) becomes the decays in place: exp(logsigmoid(z + bias) / tau).
+RLLM_API int rllm_gla_decay(float* z, const float* bias, int T, int n, float tau, void* stream) {
+  if (T <= 0 || n <= 0) return 0;
+  if (!(tau > 0.f)) return ERR_BAD_SIZE;
+  const long long total = (long long)T * n;
+  const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
+  return launch_ex(gla_decay_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, 1, z, bias, n, total, 1.f / tau);
+}
+
 // proj [T, ld] (storage type): queries at q_off, keys at k_off (H x dim each), values at v_off (H x vdim).
-// z float [T, H * dim]; zbias float [H * dim]. cu_q [S + 1]: row range of each sequence; state_slots [S]
-// (-1: the state starts at zero and is not kept). state float [slots, H, dim, vdim]. out float [T, H, vdim].
-RLLM_API int rllm_gla_scan(int dt, const void* proj, long long ld, int q_off, int k_off, int v_off, const float* z,
-                           const float* zbias, float tau, float qscale, int S, int H, int dim, int vdim,
-                           const int* cu_q, const int* state_slots, float* state, float* out, void* stream) {
-  if (S <= 0) return 0;
-  if (H <= 0 || dim <= 0 || dim > MAX_DIM || vdim <= 0 || !(tau > 0.f)) return ERR_BAD_SIZE;
+// alpha float [T, H * dim]: the decays. cu_q [S + 1]: row range of each sequence; state_slots [S] (-1: the state
+// starts at zero and is not kept). state float [slots, H, dim, vdim]. out float [T, H, vdim].
+// chunk <= 0: every sequence's rows in one CTA per (head, 32 columns). chunk > 0: the three passes over chunks of
+// that many tokens; chunk_state: float [T / chunk + S, H, dim, vdim], chunk_decay: float [T / chunk + S, H, dim].
+RLLM_API int rllm_gla_scan(int dt, const void* proj, long long ld, int q_off, int k_off, int v_off, const float* alpha,
+                           float qscale, int T, int S, int H, int dim, int vdim, const int* cu_q,
+                           const int* state_slots, float* state, float* out, int chunk, float* chunk_state,
+                           float* chunk_decay, void* stream) {
+  if (S <= 0 || T <= 0) return 0;
+  if (H <= 0 || dim <= 0 || dim > MAX_DIM || vdim <= 0) return ERR_BAD_SIZE;
   if (H > 65535 || (vdim + 31) / 32 > 65535) return ERR_TOO_LARGE;
-  dim3 grid(S, H, (vdim + 31) / 32);
+  if (dt != DT_F32 && dt != DT_BF16) return ERR_BAD_DTYPE;
   cudaStream_t s = (cudaStream_t)stream;
-  const int kp = (dim + 3) / 4;
-#define GO(TI, KP)                                                                                                 \
-  return launch_ex(gla_scan_kernel<TI, KP>, grid, dim3(128), 0, s, 1, (const TI*)proj, ld, q_off, k_off, v_off, z, \
-                   zbias, 1.f / tau, qscale, H, dim, vdim, cu_q, state_slots, state, out)
-#define BY_KP(TI)                \
-  do {                           \
-    if (kp <= 8) GO(TI, 8);      \
-    if (kp <= 16) GO(TI, 16);    \
-    if (kp <= 32) GO(TI, 32);    \
-    GO(TI, 64);                  \
-  } while (0)
-  if (dt == DT_F32) BY_KP(float);
-  if (dt == DT_BF16) BY_KP(bf16);
-#undef BY_KP
-#undef GO
-  return ERR_BAD_DTYPE;
+  const int vb = (vdim + 31) / 32;
+#define SCAN(MODE, GRID)                                                                                            \
+  (dt == DT_F32 ? scan<float, MODE>(GRID, s, proj, ld, q_off, k_off, v_off, alpha, qscale, H, dim, vdim, cu_q, S,   \
+                                    state_slots, state, out, chunk, chunk_state, chunk_decay)                       \
+                : scan<bf16, MODE>(GRID, s, proj, ld, q_off, k_off, v_off, alpha, qscale, H, dim, vdim, cu_q, S,    \
+                                   state_slots, state, out, chunk, chunk_state, chunk_decay))
+  if (chunk <= 0) return SCAN(WHOLE, dim3(S, H, vb));
+  if (!chunk_state || !chunk_decay) return ERR_BAD_SIZE;
+  const int chunks = T / chunk + S;                                  // at least as many as the sequences have
+  int rc = SCAN(LOCAL, dim3(chunks, H, vb));
+  if (rc) return rc;
+  const int per = dim * vdim;
+  rc = launch_ex(gla_carry_kernel, dim3(S, H, (per + 255) / 256), dim3(256), 0, s, 1, cu_q, state_slots, state,
+                 chunk_state, (const float*)chunk_decay, chunk, H, dim, vdim);
+  if (rc) return rc;
+  return SCAN(FINAL, dim3(chunks, H, vb));
+#undef SCAN
 }
 
 // o float [T, H, vdim]; w float [vdim]; gate in proj at g_off (H x vdim, storage type); out [T, H * vdim].

@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(256, 1)
 latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restrict__ cache, bf16* __restrict__ out,
                             const int* __restrict__ cu_q, const int* __restrict__ positions,
                             const int* __restrict__ block_table, int bt_stride, int num_seqs, int H, int rank, int dk,
-                            int ld, int page_size, float scale, int window) {
+                            int ld, int page_size, float scale, int window, int splits, float* __restrict__ pacc,
+                            float* __restrict__ pml) {
   pdl_launch();
   pdl_wait();
   // which sequence and which 64 of its (token, head) rows
@@ -231,16 +232,27 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
   const int pos_lo = positions[t_lo], pos_hi = positions[t_hi];
   const int key_first = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
   const int ntiles = (pos_hi - key_first) / KT + 1;
+  // with `splits` > 1 (steps of few rows: decoding) the key tiles are dealt out to that many CTAs, which leave
+  // their unnormalised sums, maxima and weights' sums for latent_merge_kernel
+  const int per_split = (ntiles + splits - 1) / splits;
+  const int it0 = blockIdx.y * per_split, it1 = min(ntiles, it0 + per_split);
   const int* bt = block_table + (long long)seq * bt_stride;
   const int cpr = (ld - 8) / 8;                                      // 16-byte pieces a row is filled with
+  if (it0 >= it1) {                                                  // no tile left for this CTA: it says so and goes
+    for (int r = tid; r < QROWS; r += 256) {
+      float* ml = pml + (((long long)blockIdx.x * splits + blockIdx.y) * QROWS + r) * 2;
+      ml[0] = -INFINITY; ml[1] = 0.f;
+    }
+    return;
+  }
 
   auto load_keys = [&](int it) {
-    bf16* dst = ks + (it & 1) * KT * ld;
+    bf16* dst = ks + ((it - it0) & 1) * KT * ld;
     for (int c = tid; c < KT * cpr; c += 256) {
       const int j = c / cpr, piece = c % cpr;
       const int kj = key_first + it * KT + j;
       const int page = kj <= pos_hi ? bt[kj / page_size] : -1;
-      if (piece == 0) key_ok[it & 1][j] = page >= 0;
+      if (piece == 0) key_ok[(it - it0) & 1][j] = page >= 0;
       const bool in = page >= 0 && piece * 8 < dk;
       cp_async16(dst + j * ld + piece * 8,
                  cache + (in ? ((long long)page * page_size + kj % page_size) * dk + piece * 8 : 0), in ? 16 : 0);
@@ -252,7 +264,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
     const bool in = r < nrows && piece * 8 < dk;
     cp_async16(qs + r * ld + piece * 8, qfull + (in ? ((long long)tok0 * H + row_first + r) * dk + piece * 8 : 0), in ? 16 : 0);
   }
-  load_keys(0);
+  load_keys(it0);
   asm volatile("cp.async.commit_group;" ::: "memory");
 
   // this thread's two rows (of its warp's 16): their positions and first visible keys
@@ -267,12 +279,12 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const int dk16 = (dk + 15) / 16;
 
-  for (int it = 0; it < ntiles; ++it) {
+  for (int it = it0; it < it1; ++it) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                                                 // tile `it` has landed; tile it - 1 is used up
-    if (it + 1 < ntiles) load_keys(it + 1);
+    if (it + 1 < it1) load_keys(it + 1);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    const bf16* kt = ks + (it & 1) * KT * ld;
+    const bf16* kt = ks + ((it - it0) & 1) * KT * ld;
     const int kbase = key_first + it * KT;
     if (rg_live) {
       // scores of this warp's 16 rows against its 16 keys
@@ -291,7 +303,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
           const int col = half * 16 + j * 8 + (lane & 3) * 2 + (e & 1);
           const int kj = kbase + col;
           const bool top = e < 2;
-          const bool seen = key_ok[it & 1][col] && (top ? (kj >= lo0 && kj <= pos0) : (kj >= lo1 && kj <= pos1));
+          const bool seen = key_ok[(it - it0) & 1][col] && (top ? (kj >= lo0 && kj <= pos0) : (kj >= lo1 && kj <= pos1));
           ss[(top ? r0 : r1) * (KT + 1) + col] = seen ? sc[j][e] * scale : -INFINITY;
         }
     }
@@ -335,6 +347,24 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (splits > 1) {
+    const long long pb = ((long long)blockIdx.x * splits + blockIdx.y) * QROWS;
+    if (!rg_live) {                                                  // rows nobody computed: marked empty
+      if (half == 0 && (lane & 3) == 0) { pml[(pb + r0) * 2] = -INFINITY; pml[(pb + r0) * 2 + 1] = 0.f;
+                                          pml[(pb + r1) * 2] = -INFINITY; pml[(pb + r1) * 2 + 1] = 0.f; }
+      return;
+    }
+    if (half == 0 && (lane & 3) == 0) { pml[(pb + r0) * 2] = m0; pml[(pb + r0) * 2 + 1] = l0;
+                                        pml[(pb + r1) * 2] = m1; pml[(pb + r1) * 2 + 1] = l1; }
+#pragma unroll
+    for (int n = 0; n < NH; ++n) {
+      const int col = half * NH * 8 + n * 8 + (lane & 3) * 2;
+      if (col >= rank) continue;
+      *reinterpret_cast<float2*>(pacc + (pb + r0) * rank + col) = make_float2(acc[n][0], acc[n][1]);
+      *reinterpret_cast<float2*>(pacc + (pb + r1) * rank + col) = make_float2(acc[n][2], acc[n][3]);
+    }
+    return;
+  }
   if (!rg_live) return;
   const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
   bf16* o0 = out + ((long long)tok0 * H + row_first + r0) * rank;
@@ -345,6 +375,46 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
     if (col >= rank) continue;                                       // rank is even: a pair is in or out
     if (r0 < nrows) *reinterpret_cast<__nv_bfloat162*>(o0 + col) = __floats2bfloat162_rn(acc[n][0] * i0, acc[n][1] * i0);
     if (r1 < nrows) *reinterpret_cast<__nv_bfloat162*>(o1 + col) = __floats2bfloat162_rn(acc[n][2] * i1, acc[n][3] * i1);
+  }
+}
+
+// The splits' parts of every row, merged in split order: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
+__global__ void __launch_bounds__(256)
+latent_merge_kernel(const float* __restrict__ pacc, const float* __restrict__ pml, bf16* __restrict__ out,
+                    const int* __restrict__ cu_q, int num_seqs, int H, int rank, int splits) {
+  pdl_launch();
+  pdl_wait();
+  int seq = -1, tile = 0;
+  {
+    int at = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int n = ((cu_q[s + 1] - cu_q[s]) * H + QROWS - 1) / QROWS;
+      if ((int)blockIdx.x < at + n) { seq = s; tile = blockIdx.x - at; break; }
+      at += n;
+    }
+  }
+  if (seq < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok0 = cu_q[seq], ntok = cu_q[seq + 1] - tok0;
+  const int row_first = tile * QROWS, nrows = min(QROWS, ntok * H - row_first);
+  for (int r = warp; r < nrows; r += 8) {
+    const long long pb = (long long)blockIdx.x * splits * QROWS + r;
+    const float m = lane < splits ? pml[(pb + (long long)lane * QROWS) * 2] : -INFINITY;
+    const float l = lane < splits ? pml[(pb + (long long)lane * QROWS) * 2 + 1] : 0.f;
+    const float M = warp_max(m);
+    const float w = (m == -INFINITY) ? 0.f : expf(m - M);
+    const float L = warp_sum(w * l);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    bf16* o = out + ((long long)tok0 * H + row_first + r) * rank;
+    for (int c0 = 0; c0 < rank; c0 += 32) {
+      const int col = c0 + lane;
+      float a = 0.f;
+      for (int s = 0; s < splits; ++s) {
+        const float ws = __shfl_sync(0xffffffffu, w, s);
+        if (ws != 0.f && col < rank) a = fmaf(ws, pacc[(pb + (long long)s * QROWS) * rank + col], a);
+      }
+      if (col < rank) o[col] = __float2bfloat16_rn(a * inv);
+    }
   }
 }
 
@@ -371,10 +441,12 @@ RLLM_API int rllm_latent_prepare(int dt, const void* proj, long long ld, int q_o
 
 // qfull [T, H, dk]; cache [pages * page_size, dk]; out [T, H, rank].
 // cu_q [num_seqs + 1] (row range of each sequence; null: the tensor-core kernel is not used), `tc` 0 forbids it.
+// splits > 1 (tensor-core kernel only): the keys of every row tile are dealt out to that many CTAs; pacc: float
+// [row tiles, splits, 64, rank], pml: float [row tiles, splits, 64, 2], row tiles = ceil(T * H / 64) + num_seqs.
 RLLM_API int rllm_latent_attention(int dt, const void* qfull, const void* cache, void* out, const int* token_seq,
                                    const int* positions, const int* block_table, int bt_stride, int T, int H, int rank,
                                    int dk, int page_size, float scale, int window, const int* cu_q, int num_seqs,
-                                   int tc, void* stream) {
+                                   int tc, int splits, float* pacc, float* pml, void* stream) {
   if (T <= 0) return 0;
   if (H <= 0 || rank <= 0 || rank > MAX_RANK || dk < rank || page_size <= 0) return ERR_BAD_SIZE;
   if (tc && dt == DT_BF16 && cu_q && num_seqs > 0 && dk % 8 == 0 && rank % 16 == 0 && rank <= 512 &&
@@ -383,15 +455,20 @@ RLLM_API int rllm_latent_attention(int dt, const void* qfull, const void* cache,
     const int ld = mma_row_pad(dk, nh);
     const int smem = (QROWS + 2 * KT) * ld * 2 + QROWS * (KT + 1) * 4;
     const long long blocks = ((long long)T * H + QROWS - 1) / QROWS + num_seqs;
+    if (splits < 1 || splits > 32 || (splits > 1 && (!pacc || !pml))) return ERR_BAD_SIZE;
     if (smem <= 220 * 1024 && blocks <= 2147483647LL) {
 #define GO(NH)                                                                                                          \
   do {                                                                                                                  \
     static bool done[64] = {};                                                                                          \
     const int rc = allow_dynamic_smem(latent_attention_mma_kernel<NH>, 220 * 1024, done);                               \
     if (rc) return rc;                                                                                                  \
-    return launch_ex(latent_attention_mma_kernel<NH>, dim3((unsigned)blocks), dim3(256), (size_t)smem,                  \
-                     (cudaStream_t)stream, 1, (const bf16*)qfull, (const bf16*)cache, (bf16*)out, cu_q, positions,      \
-                     block_table, bt_stride, num_seqs, H, rank, dk, ld, page_size, scale, window);                      \
+    const int rl = launch_ex(latent_attention_mma_kernel<NH>, dim3((unsigned)blocks, splits), dim3(256), (size_t)smem, \
+                             (cudaStream_t)stream, 1, (const bf16*)qfull, (const bf16*)cache, (bf16*)out, cu_q,         \
+                             positions, block_table, bt_stride, num_seqs, H, rank, dk, ld, page_size, scale, window,    \
+                             splits, pacc, pml);                                                                        \
+    if (rl || splits == 1) return rl;                                                                                   \
+    return launch_ex(latent_merge_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1,                \
+                     (const float*)pacc, (const float*)pml, (bf16*)out, cu_q, num_seqs, H, rank, splits);               \
   } while (0)
       if (nh == 4) GO(4);
       if (nh == 8) GO(8);

@@ -44,6 +44,7 @@ class Backend:
         if self.device.type != "cuda":
             raise ops.KernelError("the engine runs on a CUDA device only (there is no CPU path)")
         self.fast = dtype == torch.bfloat16 and os.environ.get("RLLM_B200_GENERIC_ONLY") != "1"
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._sm100 = None
         if self.fast:
             from . import sm100          # builds/loads the tcgen05 library, or raises
@@ -224,9 +225,20 @@ class Backend:
         return self._mix.latent_prepare(*a, **k)
 
     def latent_attention(self, qfull, cache, ctx, rank, scale, window):
+        # Steps of few rows (decoding) have fewer row tiles than the GPU has SMs: the keys of a tile are then
+        # dealt out to several CTAs, at least four key tiles (128 keys) each. Everything this depends on is
+        # known when a decode graph is captured (rows, sequences, the bound of the key count).
+        T, H = qfull.shape[0], qfull.shape[1]
+        tiles = (T * H + 63) // 64 + ctx.num_seqs
+        keys = min(window, ctx.max_kv_len) if window else ctx.max_kv_len
+        splits = max(1, min(16, self.sm_count // tiles, keys // 128))
         return self._mix.latent_attention(qfull, cache.tensors["kv"], ctx.token_seq, ctx.positions,
                                           cache.block_table, rank, scale, window, cu_q=ctx.cu_q, num_seqs=ctx.num_seqs,
-                                          tensor_cores=self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1")
+                                          tensor_cores=self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1",
+                                          splits=splits)
+
+    def gla_decay(self, z, bias, tau):
+        return self._mix.gla_decay(z, bias, tau)
 
     def gla_scan(self, *a, **k):
         return self._mix.gla_scan(*a, **k)

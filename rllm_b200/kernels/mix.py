@@ -30,9 +30,10 @@ ops.register_signatures("mix", {
     "rllm_latent_prepare": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_float, _P,
                             _P, _P, _P, _P],
     "rllm_latent_attention": [c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                              c_int, _P, c_int, c_int, _P],
-    "rllm_gla_scan": [c_int, _P, _LL, c_int, c_int, c_int, _P, _P, c_float, c_float, c_int, c_int, c_int, c_int,
-                      _P, _P, _P, _P, _P],
+                              c_int, _P, c_int, c_int, c_int, _P, _P, _P],
+    "rllm_gla_decay": [_P, _P, c_int, c_int, c_float, _P],
+    "rllm_gla_scan": [c_int, _P, _LL, c_int, c_int, c_int, _P, c_float, c_int, c_int, c_int, c_int, c_int, _P, _P, _P,
+                      _P, c_int, _P, _P, _P],
     "rllm_gla_finish": [c_int, _P, _P, c_float, _P, _LL, c_int, c_int, c_int, c_int, _P, _P],
 })
 
@@ -202,10 +203,12 @@ def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: int, heads: int, dim
 
 def latent_attention(qfull: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                      block_table: torch.Tensor, rank: int, scale: float, window: int | None,
-                     cu_q: torch.Tensor | None = None, num_seqs: int = 0, tensor_cores: bool = True) -> torch.Tensor:
+                     cu_q: torch.Tensor | None = None, num_seqs: int = 0, tensor_cores: bool = True,
+                     splits: int = 1) -> torch.Tensor:
     """qfull [T, heads, dk]; cache [pages, page, dk] -> [T, heads, rank] of qfull's dtype. With `cu_q`
     (int32 [num_seqs + 1], the row range of each sequence) bfloat16 problems of fitting sizes run on the
-    tensor cores (`tensor_cores` False: never)."""
+    tensor cores (`tensor_cores` False: never); `splits` > 1 there deals a row tile's keys out to that many
+    CTAs and merges their parts (steps of few rows)."""
     _cuda(qfull, "qfull"); _cuda(cache, "cache")
     T, H, dk = qfull.shape
     if not qfull.is_contiguous() or not cache.is_contiguous() or cache.dtype != qfull.dtype or cache.dim() != 3 \
@@ -218,24 +221,41 @@ def latent_attention(qfull: torch.Tensor, cache: torch.Tensor, token_seq: torch.
     if cu_q is not None:
         _i32(cu_q, "cu_q", num_seqs + 1)
     out = torch.empty((T, H, rank), dtype=qfull.dtype, device=qfull.device)
+    pacc = pml = None
+    splits = max(1, min(int(splits), 32))
+    if splits > 1 and cu_q is not None:
+        tiles = (T * H + 63) // 64 + num_seqs
+        pacc = torch.empty((tiles, splits, 64, rank), dtype=torch.float32, device=qfull.device)
+        pml = torch.empty((tiles, splits, 64, 2), dtype=torch.float32, device=qfull.device)
+    else:
+        splits = 1
     _check(_fn("mix", "rllm_latent_attention")(
         _dt(qfull, "qfull"), qfull.data_ptr(), cache.data_ptr(), out.data_ptr(), token_seq.data_ptr(),
         positions.data_ptr(), block_table.data_ptr(), block_table.stride(0), T, H, rank, dk, cache.shape[1],
-        float(scale), int(window or 0), _ptr(cu_q), int(num_seqs), int(bool(tensor_cores)), _stream()),
-        "latent_attention")
+        float(scale), int(window or 0), _ptr(cu_q), int(num_seqs), int(bool(tensor_cores)), splits, _ptr(pacc),
+        _ptr(pml), _stream()), "latent_attention", 2 if splits > 1 else 1)
     return out
 
 
 # --------------------------------------------------------------------------- gated linear attention
 
-def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Tensor, zbias: torch.Tensor,
-             tau: float, qscale: float, heads: int, dim: int, vdim: int, cu_q: torch.Tensor, num_seqs: int,
-             state_slots: torch.Tensor | None, state: torch.Tensor) -> torch.Tensor:
-    """See csrc/gla.cu. -> float32 [T, heads, vdim]; `state` float32 [slots, heads, dim, vdim] is updated."""
+def gla_decay(z: torch.Tensor, bias: torch.Tensor, tau: float) -> torch.Tensor:
+    """z float32 [T, n] -> the decays sigmoid(z + bias)^(1/tau), in place."""
+    _f32(z, "decay logits")
+    _f32(bias, "decay bias", (z.shape[1],))
+    _check(_fn("mix", "rllm_gla_decay")(z.data_ptr(), bias.data_ptr(), z.shape[0], z.shape[1], float(tau), _stream()),
+           "gla_decay")
+    return z
+
+
+def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, alpha: torch.Tensor, qscale: float, heads: int,
+             dim: int, vdim: int, cu_q: torch.Tensor, num_seqs: int, state_slots: torch.Tensor | None,
+             state: torch.Tensor, chunk: int = 0) -> torch.Tensor:
+    """See csrc/gla.cu. -> float32 [T, heads, vdim]; `state` float32 [slots, heads, dim, vdim] is updated.
+    `chunk` > 0: sequences are cut into chunks of that many tokens that run side by side (long portions)."""
     T = proj.shape[0]
     _rows(proj, "proj", max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim))
-    _f32(z, "decay logits", (T, heads * dim))
-    _f32(zbias, "decay bias", (heads * dim,))
+    _f32(alpha, "decays", (T, heads * dim))
     _f32(state, "state")
     if state.dim() != 4 or tuple(state.shape[1:]) != (heads, dim, vdim):
         raise KernelError(f"state must be [slots, {heads}, {dim}, {vdim}], got {list(state.shape)}")
@@ -243,10 +263,15 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Te
     if state_slots is not None:
         _i32(state_slots, "state_slots", num_seqs)
     out = torch.empty((T, heads, vdim), dtype=torch.float32, device=proj.device)
+    cs = cd = None
+    if chunk > 0:
+        n = T // chunk + num_seqs
+        cs = torch.empty((n, heads, dim, vdim), dtype=torch.float32, device=proj.device)
+        cd = torch.empty((n, heads, dim), dtype=torch.float32, device=proj.device)
     _check(_fn("mix", "rllm_gla_scan")(
-        _dt(proj, "proj"), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, z.data_ptr(), zbias.data_ptr(),
-        float(tau), float(qscale), num_seqs, heads, dim, vdim, cu_q.data_ptr(), _ptr(state_slots), state.data_ptr(),
-        out.data_ptr(), _stream()), "gla_scan")
+        _dt(proj, "proj"), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, alpha.data_ptr(), float(qscale), T,
+        num_seqs, heads, dim, vdim, cu_q.data_ptr(), _ptr(state_slots), state.data_ptr(), out.data_ptr(), int(chunk),
+        _ptr(cs), _ptr(cd), _stream()), "gla_scan", 3 if chunk > 0 else 1)
     return out
 
 

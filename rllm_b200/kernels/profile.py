@@ -182,12 +182,15 @@ class OpProfile:
         return self._timed("latent_attention", nbytes, 2 * H * (dk + rank) * pairs, self._be.latent_attention,
                            qfull, cache, ctx, rank, scale, window)
 
-    def gla_scan(self, proj, q_off, k_off, v_off, z, zbias, tau, qscale, heads, dim, vdim, cu_q, num_seqs, slots, state):
+    def gla_decay(self, z, bias, tau):
+        return self._timed("gla_decay", 2 * _nbytes(z), 0, self._be.gla_decay, z, bias, tau)
+
+    def gla_scan(self, proj, q_off, k_off, v_off, alpha, qscale, heads, dim, vdim, cu_q, num_seqs, slots, state, chunk=0):
         T = proj.shape[0]
-        nbytes = T * heads * (2 * dim + vdim) * proj.element_size() + _nbytes(z) + T * heads * vdim * 4 \
+        nbytes = T * heads * (2 * dim + vdim) * proj.element_size() + _nbytes(alpha) + T * heads * vdim * 4 \
             + 2 * num_seqs * heads * dim * vdim * 4
-        return self._timed("gla_scan", nbytes, 5 * T * heads * dim * vdim, self._be.gla_scan, proj, q_off, k_off, v_off, z,
-                           zbias, tau, qscale, heads, dim, vdim, cu_q, num_seqs, slots, state)
+        return self._timed("gla_scan", nbytes, 5 * T * heads * dim * vdim, self._be.gla_scan, proj, q_off, k_off, v_off,
+                           alpha, qscale, heads, dim, vdim, cu_q, num_seqs, slots, state, chunk)
 
     def gla_finish(self, o, *a, **k):
         return self._timed("gla_finish", 2 * _nbytes(o), 0, self._be.gla_finish, o, *a, **k)

@@ -26,6 +26,7 @@ class GatedLinearAttention(Part):
                  decay_rank: int | None = None):
         self.hidden, self.heads, self.dim, self.vdim = hidden, heads, dim, vdim
         self.tau, self.eps, self.decay_rank = float(tau), float(eps), decay_rank
+        self.chunk = 128         # tokens per chunk of a long portion
         self.w_in = self.w_a2 = self.b_a2 = self.w_norm = self.w_o = None
 
     def params(self):
@@ -53,8 +54,12 @@ class GatedLinearAttention(Part):
         H, d, v = self.heads, self.dim, self.vdim
         proj = be.linear(x, self.w_in)                                   # [T, q | k | v | gate | a1]
         z = be.linear_f32(proj[:, self._a1_off:], self.w_a2)             # float decay logits [T, H * dim]
-        o = be.gla_scan(proj, 0, H * d, 2 * H * d, z, self._b_f32, self.tau, d ** -0.5, H, d, v, ctx.cu_q,
-                        ctx.num_seqs, ctx.state_slots, cache.state["S"])
+        alpha = be.gla_decay(z, self._b_f32, self.tau)                   # in place
+        # long portions are cut into chunks that run side by side (the host knows a step's longest portion;
+        # inside a decode graph it is one token)
+        chunk = self.chunk if not ctx.graph_safe and ctx.max_q_len >= 3 * self.chunk else 0
+        o = be.gla_scan(proj, 0, H * d, 2 * H * d, alpha, d ** -0.5, H, d, v, ctx.cu_q, ctx.num_seqs,
+                        ctx.state_slots, cache.state["S"], chunk)
         att = be.gla_finish(o, self._norm_f32, self.eps, proj, 2 * H * d + H * v)
         if residual is None:
             return be.linear_f32(att, self.w_o)

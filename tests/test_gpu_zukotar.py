@@ -253,6 +253,38 @@ def test_latent_attention_over_steps(dtype, m, page):
     assert rel(again, want_b) < tol
 
 
+@pytest.mark.parametrize("window", [None, 300])
+def test_latent_decoding_deals_the_keys_out_to_several_ctas(window):
+    """Single tokens of two sequences against 600 and 260 cached keys in bfloat16: the row tiles' keys are
+    split over CTAs whose parts are merged; one far key (position 7) and one at the window's edge are made
+    to win their scores."""
+    from rllm_b200.parts import InterleavedRotary, LatentAttention
+    W, dtype = 48, "bfloat16"
+    m = Z.latent(16, 16, 16, 24, 64, 0.2, 10000.0, 16, window)
+    w = latent_weights(W, m, seed=77)
+    ha, hb = rnd(606, W, seed=1), rnd(266, W, seed=2)
+    for p in (7, 606 - 300, 606 - 301):
+        ha[p] *= 6.0
+    want = {k: P.latent_attention(x.to(DT[dtype]).double(), as_stored(w, dtype), "x.", m, 1e-6) for k, x in (("a", ha), ("b", hb))}
+    part = LatentAttention(W, 16, 16, 16, 24, 64, 0.2, InterleavedRotary(16, 10000.0, 16), window=window, eps=1e-6)
+    bind(part, w, dtype, "x.")
+    da, db = ha.to(DT[dtype]).to(DEV), hb.to(DT[dtype]).to(DEV)
+    hs = Harness(dtype, [part.cache_spec()], page_size=16, pages=64)
+    y = hs.run([("a", 600), ("b", 260)], lambda ctx, cache: part.forward(torch.cat([da[:600], db[:260]]), ctx, cache))
+    assert rel(y[:600], want["a"][:600]) < 2.5e-2 and rel(y[600:], want["b"][:260]) < 2.5e-2
+    seen = []
+    for i in range(6):
+        def step(ctx, cache):
+            T, H = 2, 16
+            tiles = (T * H + 63) // 64 + ctx.num_seqs
+            keys = min(window, ctx.max_kv_len) if window else ctx.max_kv_len
+            seen.append(max(1, min(16, ctx.backend.sm_count // tiles, keys // 128)))
+            return part.forward(torch.cat([da[600 + i: 601 + i], db[260 + i: 261 + i]]), ctx, cache)
+        y = hs.run([("a", 1), ("b", 1)], step)
+        assert rel(y[:1], want["a"][600 + i: 601 + i]) < 2.5e-2 and rel(y[1:], want["b"][260 + i: 261 + i]) < 2.5e-2
+    assert min(seen) >= 2            # the steps above did run with their keys split
+
+
 @pytest.mark.parametrize("dtype", list(DT))
 @pytest.mark.parametrize("H,d,v,tau,r", [(3, 20, 24, 6.0, 8), (1, 64, 72, 2.5, 16), (2, 36, 44, 16.0, 8), (2, 130, 33, 40.0, 4)])
 def test_gla_over_steps_and_slots(dtype, H, d, v, tau, r):
@@ -300,6 +332,40 @@ def test_gla_over_steps_and_slots(dtype, H, d, v, tau, r):
         hs.cache.check()
     if dtype == "float32":
         assert all(torch.equal(outs["whole"], o) for o in outs.values())
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_gla_long_portions_run_in_chunks_side_by_side(dtype):
+    """Portions long enough for the chunked passes (several chunks, a last one that is not full, two sequences
+    of unequal length in one step, one of them with a state from an earlier step), then single tokens that
+    continue from the state the chunked passes left."""
+    from rllm_b200.parts import GatedLinearAttention
+    W, H, d, v, r, tau = 32, 2, 24, 40, 8, 30.0
+    shapes = {"q": (H * d, W), "k": (H * d, W), "v": (H * v, W), "g": (H * v, W), "a1": (r, W), "a2": (H * d, r),
+              "a2.b": (H * d,), "norm": (v,), "o": (W, H * v)}
+    w = {"x." + k: rnd(*s, seed=i + 50, scale=0.2) for i, (k, s) in enumerate(shapes.items())}
+    w["x.norm"] = w["x.norm"] + 1
+    w["x.a2.b"] = w["x.a2.b"] * 3 + 2.0
+    part = GatedLinearAttention(W, H, d, v, tau, eps=1e-5, decay_rank=r)
+    bind(part, w, dtype, "x.")
+    assert part.chunk == 128
+    m = {"heads": H, "dim": d, "vdim": v, "tau": tau}
+    seqs = {"a": rnd(30 + 500 + 4, W, seed=60), "b": rnd(130 + 3, W, seed=61)}
+    seqs["a"][31] *= 8.0
+    want = {k: P.gla(x.to(DT[dtype]).double(), as_stored(w, dtype), "x.", m, 1e-5) for k, x in seqs.items()}
+    dev = {k: x.to(DT[dtype]).to(DEV) for k, x in seqs.items()}
+    hs = Harness(dtype, [part.cache_spec()], slots=2)
+    got = {"a": [], "b": []}
+    got["a"].append(hs.run([("a", 30)], lambda ctx, cache: part.forward(dev["a"][:30], ctx, cache)))
+    y = hs.run([("a", 500), ("b", 130)], lambda ctx, cache: part.forward(torch.cat([dev["a"][30:530], dev["b"][:130]]), ctx, cache))
+    got["a"].append(y[:500]); got["b"].append(y[500:])
+    for i in range(3):
+        y = hs.run([("b", 1), ("a", 1)], lambda ctx, cache: part.forward(
+            torch.cat([dev["b"][130 + i: 131 + i], dev["a"][530 + i: 531 + i]]), ctx, cache))
+        got["b"].append(y[:1]); got["a"].append(y[1:])
+    got["a"].append(hs.run([("a", 1)], lambda ctx, cache: part.forward(dev["a"][533:], ctx, cache)))
+    tol = 2e-5 if dtype == "float32" else 2.5e-2
+    assert rel(torch.cat(got["a"]), want["a"]) < tol and rel(torch.cat(got["b"]), want["b"]) < tol
 
 
 @pytest.mark.parametrize("dtype", list(DT))
