@@ -6,6 +6,10 @@ ranges of keys) were tuned with, and the small case a profiler is pointed at.
     python -m rllm_b200.kernels.microbench attn-decode --batch 64 --context 3000 --splits 1,2,3
     python -m rllm_b200.kernels.microbench attn-prefill --tokens 2048 --kernel tc
     python -m rllm_b200.kernels.microbench sample --rows 8 --top-p 0.9
+    python -m rllm_b200.kernels.microbench experts --tokens 8,2048 --width 2048 --ff 2048 --experts 16 --top 6
+    python -m rllm_b200.kernels.microbench latent-attn --heads 16 --rank 512 --rot 64 --tokens 2048
+    python -m rllm_b200.kernels.microbench latent-attn --heads 16 --rank 512 --rot 64 --batch 8 --context 1024
+    python -m rllm_b200.kernels.microbench gla --heads 16 --dim 128 --vdim 128 --tokens 2048 [--batch 8]
     ... --plain 3      # no timing: three plain launches and a synchronize (for ncu -k ... -c ...)
 
 Timing: the kernel runs back to back over `--copies` distinct weight (or cache) tensors, larger
@@ -193,6 +197,77 @@ def cmd_sample(a) -> None:
     run([f] * 4, a.plain, f"sample rows={R} vocab={V} {what}", nbytes=R * V * 4)
 
 
+def cmd_experts(a) -> None:
+    """The two grouped products of a routed feed-forward (bfloat16) over a plan from random router logits."""
+    from . import mix
+    W, F, E, top = a.width, a.ff, a.experts, a.top
+    ups = [torch.randn(E, F, W, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(a.copies)]
+    downs = [torch.randn(E, W, F, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(a.copies)]
+    for T in a.tokens:
+        x = torch.randn(T, W, device=DEV, dtype=torch.bfloat16)
+        logits = torch.randn(T, E, device=DEV)
+        per_tile = min(mix.tile_rows(torch.bfloat16, W, W), mix.tile_rows(torch.bfloat16, F, F))
+        idx, wt = mix.moe_topk(logits, top, a.groups, a.keep)
+        plan = mix.moe_plan(idx, wt, E, per_tile)
+        act = torch.empty(T * top, F, device=DEV, dtype=torch.bfloat16)
+        out = torch.empty(T * top, W, device=DEV, dtype=torch.float32)
+        used = int(torch.unique(idx).numel())
+        run([lambda: (mix.moe_topk(logits, top, a.groups, a.keep), mix.moe_plan(idx, wt, E, per_tile))], a.plain,
+            f"route+plan T={T}")
+        run([lambda u=u: mix.grouped_gemm_ragged(x, u, plan, act, mix.GEPI_RELU2, gather=True) for u in ups], a.plain,
+            f"experts_up T={T} ({used} experts used)", used * F * W * 2 + T * top * (F + W) * 2, 2.0 * T * top * F * W)
+        run([lambda d=d: mix.grouped_gemm_ragged(act, d, plan, out, mix.GEPI_STORE_F32, scatter=True, scale=True)
+             for d in downs], a.plain, f"experts_down T={T}", used * F * W * 2 + T * top * (2 * F + 4 * W),
+            2.0 * T * top * F * W)
+
+
+def _paged(batch: int, context: int, new: int, page: int):
+    """Block tables, positions and row ranges of `batch` sequences that hold `context` keys, the last `new` of
+    them this step's tokens; pages handed out in a random order."""
+    per = (context + page - 1) // page
+    perm = torch.randperm(batch * per, dtype=torch.int32).view(batch, per)
+    pos = torch.arange(context - new, context, dtype=torch.int32).repeat(batch)
+    seq = torch.arange(batch, dtype=torch.int32).repeat_interleave(new)
+    cu = torch.arange(batch + 1, dtype=torch.int32) * new
+    return perm.to(DEV), pos.to(DEV), seq.to(DEV), cu.to(DEV), batch * per
+
+
+def cmd_latent_attn(a) -> None:
+    from . import mix
+    H, rank, dk, page = a.heads, a.rank, a.rank + a.rot, a.page
+    cases = [(1, T, T) for T in a.tokens] if a.batch == 0 else [(a.batch, a.context, 1)]
+    for batch, context, new in cases:
+        bt, pos, seq, cu, pages = _paged(batch, context, new, page)
+        caches = [torch.randn(pages, page, dk, device=DEV, dtype=torch.bfloat16) for _ in range(a.copies)]
+        q = torch.randn(batch * new, H, dk, device=DEV, dtype=torch.bfloat16)
+        tiles = (batch * new * H + 63) // 64 + batch
+        keys = min(a.window, context) if a.window else context
+        splits = a.splits or max(1, min(16, torch.cuda.get_device_properties(0).multi_processor_count // tiles, keys // 128))
+        seen = sum(min(p + 1, a.window or p + 1) for p in range(context - new, context)) * batch
+        run([lambda c=c: mix.latent_attention(q, c, seq, pos, bt, rank, dk ** -0.5, a.window or None, cu_q=cu,
+                                              num_seqs=batch, tensor_cores=not a.simt, splits=splits) for c in caches],
+            a.plain, f"latent attention {batch} x {new} tokens, context {context}, {H} heads, splits {splits}",
+            batch * min(context, keys + new) * dk * 2 + 2 * q.numel() * 2, 2.0 * H * (dk + rank) * seen)
+
+
+def cmd_gla(a) -> None:
+    from . import mix
+    H, d, v = a.heads, a.dim, a.vdim
+    cases = [(1, T) for T in a.tokens] if a.batch == 0 else [(a.batch, 1)]
+    for batch, new in cases:
+        T = batch * new
+        cols = 2 * H * d + H * v
+        proj = torch.randn(T, cols, device=DEV, dtype=torch.bfloat16) * 0.3
+        alpha = torch.rand(T, H * d, device=DEV) * 0.1 + 0.9
+        cu = (torch.arange(batch + 1, dtype=torch.int32) * new).to(DEV)
+        slots = torch.arange(batch, dtype=torch.int32).to(DEV)
+        states = [torch.zeros(batch, H, d, v, device=DEV) for _ in range(a.copies if new == 1 else 1)]
+        chunk = a.chunk if new >= 3 * a.chunk else 0
+        run([lambda s=s: mix.gla_scan(proj, 0, H * d, 2 * H * d, alpha, d ** -0.5, H, d, v, cu, batch, slots, s, chunk)
+             for s in states], a.plain, f"gla scan {batch} x {new} tokens, {H} heads of {d} x {v}, chunk {chunk}",
+            T * (cols * 2 + H * d * 4 + H * v * 4) + 2 * batch * H * d * v * 4, (5.0 if chunk == 0 else 8.0) * T * H * d * v)
+
+
 def main(argv=None) -> int:
     ints = lambda s: [int(x) for x in s.split(",")]
     ap = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
@@ -205,6 +280,26 @@ def main(argv=None) -> int:
     p.add_argument("--top-k", type=int, default=0)
     p.add_argument("--top-p", type=float, default=1.0)
     p.add_argument("--min-p", type=float, default=0.0)
+    p = sub.add_parser("experts")
+    p.add_argument("--plain", type=int, default=0)
+    p.add_argument("--copies", type=int, default=4)
+    p.add_argument("--tokens", type=ints, default=[8, 2048])
+    for k, v in (("width", 2048), ("ff", 2048), ("experts", 16), ("top", 6), ("groups", 1), ("keep", 1)):
+        p.add_argument("--" + k, type=int, default=v)
+    p = sub.add_parser("latent-attn")
+    p.add_argument("--plain", type=int, default=0)
+    p.add_argument("--copies", type=int, default=4)
+    p.add_argument("--tokens", type=ints, default=[2048])
+    for k, v in (("heads", 16), ("rank", 512), ("rot", 64), ("page", 16), ("batch", 0), ("context", 1024), ("window", 0),
+                 ("splits", 0)):
+        p.add_argument("--" + k, type=int, default=v)
+    p.add_argument("--simt", action="store_true", help="the CUDA-core kernel")
+    p = sub.add_parser("gla")
+    p.add_argument("--plain", type=int, default=0)
+    p.add_argument("--copies", type=int, default=8)
+    p.add_argument("--tokens", type=ints, default=[2048])
+    for k, v in (("heads", 16), ("dim", 128), ("vdim", 128), ("batch", 0), ("chunk", 128)):
+        p.add_argument("--" + k, type=int, default=v)
     for name in ("gemm", "attn-decode", "attn-prefill"):
         p = sub.add_parser(name)
         p.add_argument("--plain", type=int, default=0, help="N plain launches instead of timing")
@@ -240,7 +335,8 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print("microbench: no CUDA device", file=sys.stderr)
         return 1
-    {"gemm": cmd_gemm, "attn-decode": cmd_attn_decode, "attn-prefill": cmd_attn_prefill, "sample": cmd_sample}[a.cmd](a)
+    {"gemm": cmd_gemm, "attn-decode": cmd_attn_decode, "attn-prefill": cmd_attn_prefill, "sample": cmd_sample,
+     "experts": cmd_experts, "latent-attn": cmd_latent_attn, "gla": cmd_gla}[a.cmd](a)
     return 0
 
 
