@@ -16,11 +16,10 @@
 // gate g: the result is multiplied by sigmoid(g) (uniform mode).
 //
 // bfloat16 problems whose rows are 16-byte aligned (K, strides and offsets multiples of 8) run on the
-// tensor cores instead (grouped_gemm_mma_kernel): tiles of 128 rows x 128 weight rows x 32 of K, eight warps
-// of 64 x 32 each, `mma.sync` m16n8k16 with float accumulators, operands brought by `cp.async` (gathered rows
-// included) through a ring of three stages and read with `ldmatrix`; a warp leaves out the row tiles of 16
-// that lie beyond the tile's rows, so that a tile with a few rows (decoding) costs its weights' way through
-// the ring and little else. K runs in ascending blocks of 16 inside one accumulator: a row's result is the
+// tensor cores instead (grouped_gemm_mma_kernel, in a shape for long and one for short row lists):
+// `mma.sync` m16n8k16 with float accumulators, operands brought by `cp.async` (gathered rows included) through
+// a ring of stages and read with `ldmatrix`; a warp leaves out the row tiles of 16 that lie beyond the tile's
+// rows, so that a tile with a few rows costs its weights' way through the ring and little else. K runs in ascending blocks of 16 inside one accumulator: a row's result is the
 // same wherever it stands. The float path keeps to FMA.
 #include "common.cuh"
 using namespace rllm;
@@ -119,8 +118,13 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const GroupedArgs p) 
 }
 
 // ------------------------------------------------------------------------------------------ tensor cores
-constexpr int MB = 128, MN = 128, MK = 32, MSTAGES = 3, MLD = MK + 8;   // 80-byte rows: ldmatrix meets 8 bank groups
-constexpr int MMA_SMEM = MSTAGES * (MB + MN) * MLD * 2;
+// Two shapes of the kernel: LONG for tiles of up to 128 rows (prompt portions: 128 x 128 x 32, three stages,
+// eight warps of 64 x 32), FEW for tiles of up to 32 rows (decoding: what counts is the weights' way through
+// the ring, so 256 contiguous bytes of a weight row per copy step, four stages, tiles of 64 weight rows so
+// that there are CTAs for every SM; four warps of 32 x 16).
+struct LongTile { static constexpr int BM = 128, BN = 128, BK = 32, ST = 3, WM = 2, WN = 4; };
+struct FewTile { static constexpr int BM = 32, BN = 64, BK = 128, ST = 4, WM = 1, WN = 4; };
+template <typename C> constexpr int mma_smem() { return C::ST * (C::BM + C::BN) * (C::BK + 8) * 2; }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -137,74 +141,79 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int EPI>
-__global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const GroupedArgs p) {
+template <int EPI, typename C>
+__global__ void __launch_bounds__(C::WM * C::WN * 32) grouped_gemm_mma_kernel(const GroupedArgs p) {
   pdl_launch();
   pdl_wait();
+  constexpr int BM_ = C::BM, BN_ = C::BN, BK_ = C::BK, ST_ = C::ST, THREADS = C::WM * C::WN * 32;
+  constexpr int LDS = BK_ + 8;                                        // rows 16 bytes apart in the banks: ldmatrix meets 8 bank groups
+  constexpr int MT = BM_ / C::WM / 16, NT = BN_ / C::WN / 8;          // row tiles of 16 and column tiles of 8 a warp
+  constexpr int CPR = BK_ / 8;                                        // 16-byte pieces of a row per block of K
+  static_assert(NT % 2 == 0 && (BM_ * CPR) % THREADS == 0 && (BN_ * CPR) % THREADS == 0, "tile shape");
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* As = reinterpret_cast<bf16*>(smem_raw);                      // [MSTAGES][MB][MLD]
-  bf16* Bs = As + MSTAGES * MB * MLD;                                // [MSTAGES][MN][MLD]
-  __shared__ int arow[MB];
+  bf16* As = reinterpret_cast<bf16*>(smem_raw);                      // [ST][BM][LDS]
+  bf16* Bs = As + ST_ * BM_ * LDS;                                   // [ST][BN][LDS]
+  __shared__ int arow[BM_];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wm = warp >> 2, wn = warp & 3;                           // 2 x 4 warps, 64 x 32 each
+  const int wm = warp / C::WN, wn = warp % C::WN;
   int g, row0, rows;
   if (p.tiles) {
     if ((int)blockIdx.y >= *p.n_tiles) return;
     g = p.tiles[3 * blockIdx.y]; row0 = p.tiles[3 * blockIdx.y + 1]; rows = p.tiles[3 * blockIdx.y + 2];
   } else {
-    g = blockIdx.z; row0 = blockIdx.y * MB; rows = min(MB, p.T - row0);
+    g = blockIdx.z; row0 = blockIdx.y * BM_; rows = min(BM_, p.T - row0);
   }
-  const int n0 = blockIdx.x * MN;
+  const int n0 = blockIdx.x * BN_;
   const bf16* A = (const bf16*)p.A + (p.tiles ? 0 : (long long)g * p.a_gs);
   const bf16* B = (const bf16*)p.B + (long long)g * p.b_gs;
-  if (tid < MB) arow[tid] = tid < rows ? (p.rows_in ? p.rows_in[row0 + tid] : row0 + tid) : -1;
+  for (int r = tid; r < BM_; r += THREADS) arow[r] = r < rows ? (p.rows_in ? p.rows_in[row0 + r] : row0 + r) : -1;
   __syncthreads();
 
-  // this thread's two 16-byte pieces of each operand per stage: rows tid/4 and tid/4 + 64, 8 of K at (tid%4)*8
-  const int lrow = tid >> 2, lk = (tid & 3) * 8;
-  const long long a0 = arow[lrow] < 0 ? -1 : (long long)arow[lrow] * p.lda;
-  const long long a1 = arow[lrow + 64] < 0 ? -1 : (long long)arow[lrow + 64] * p.lda;
-  const long long b0 = n0 + lrow < p.N ? (long long)(n0 + lrow) * p.K : -1;
-  const long long b1 = n0 + lrow + 64 < p.N ? (long long)(n0 + lrow + 64) * p.K : -1;
-  const int nk = (p.K + MK - 1) / MK;
+  const int nk = (p.K + BK_ - 1) / BK_;
   auto load = [&](int kb) {
-    const int st = kb % MSTAGES, k = kb * MK + lk;
-    const int bytes = k < p.K ? 16 : 0;                              // K is a multiple of 8: a piece is whole or empty
-    bf16* as = As + (st * MB + lrow) * MLD + lk;
-    bf16* bs = Bs + (st * MN + lrow) * MLD + lk;
-    cp_async16(as, A + (a0 < 0 || !bytes ? 0 : a0 + k), a0 < 0 ? 0 : bytes);
-    cp_async16(as + 64 * MLD, A + (a1 < 0 || !bytes ? 0 : a1 + k), a1 < 0 ? 0 : bytes);
-    cp_async16(bs, B + (b0 < 0 || !bytes ? 0 : b0 + k), b0 < 0 ? 0 : bytes);
-    cp_async16(bs + 64 * MLD, B + (b1 < 0 || !bytes ? 0 : b1 + k), b1 < 0 ? 0 : bytes);
-  };
-  float acc[4][4][4] = {};
-  // row tiles of 16 this warp has to compute
-  const int mt_live = min(4, max(0, (rows - wm * 64 + 15) / 16));
+    const int st = kb % ST_;
 #pragma unroll
-  for (int s = 0; s < MSTAGES - 1; ++s) {
+    for (int i = 0; i < BM_ * CPR / THREADS; ++i) {
+      const int c = tid + i * THREADS, r = c / CPR, k = kb * BK_ + (c % CPR) * 8;
+      const int ar = arow[r];
+      const bool in = ar >= 0 && k < p.K;                            // K is a multiple of 8: a piece is whole or empty
+      cp_async16(As + (st * BM_ + r) * LDS + (c % CPR) * 8, A + (in ? (long long)ar * p.lda + k : 0), in ? 16 : 0);
+    }
+#pragma unroll
+    for (int i = 0; i < BN_ * CPR / THREADS; ++i) {
+      const int c = tid + i * THREADS, r = c / CPR, k = kb * BK_ + (c % CPR) * 8;
+      const bool in = n0 + r < p.N && k < p.K;
+      cp_async16(Bs + (st * BN_ + r) * LDS + (c % CPR) * 8, B + (in ? (long long)(n0 + r) * p.K + k : 0), in ? 16 : 0);
+    }
+  };
+  float acc[MT][NT][4] = {};
+  // row tiles of 16 this warp has to compute: those beyond the tile's rows are left out
+  const int mt_live = min(MT, max(0, (rows - wm * MT * 16 + 15) / 16));
+#pragma unroll
+  for (int s = 0; s < ST_ - 1; ++s) {
     if (s < nk) load(s);
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   for (int kb = 0; kb < nk; ++kb) {
-    asm volatile("cp.async.wait_group %0;" ::"n"(MSTAGES - 2) : "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(ST_ - 2) : "memory");
     __syncthreads();                                                 // block kb has landed; block kb - 1 is used up
-    if (kb + MSTAGES - 1 < nk) load(kb + MSTAGES - 1);
+    if (kb + ST_ - 1 < nk) load(kb + ST_ - 1);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    const bf16* as = As + (kb % MSTAGES) * MB * MLD;
-    const bf16* bs = Bs + (kb % MSTAGES) * MN * MLD;
+    const bf16* as = As + (kb % ST_) * BM_ * LDS;
+    const bf16* bs = Bs + (kb % ST_) * BN_ * LDS;
 #pragma unroll
-    for (int kk = 0; kk < MK; kk += 16) {
-      unsigned bfrag[2][4];
+    for (int kk = 0; kk < BK_; kk += 16) {
+      unsigned bfrag[NT / 2][4];
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
-        ldmatrix4(bfrag[j], bs + (wn * 32 + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * MLD + kk + ((lane >> 3) & 1) * 8);
+      for (int j = 0; j < NT / 2; ++j)
+        ldmatrix4(bfrag[j], bs + (wn * NT * 8 + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * LDS + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < MT; ++i) {
         if (i < mt_live) {
           unsigned afrag[4];
-          ldmatrix4(afrag, as + (wm * 64 + i * 16 + (lane & 15)) * MLD + kk + (lane >> 4) * 8);
+          ldmatrix4(afrag, as + (wm * MT * 16 + i * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) mma16816(acc[i][j], afrag, bfrag[j >> 1][(j & 1) * 2], bfrag[j >> 1][(j & 1) * 2 + 1]);
+          for (int j = 0; j < NT; ++j) mma16816(acc[i][j], afrag, bfrag[j >> 1][(j & 1) * 2], bfrag[j >> 1][(j & 1) * 2 + 1]);
         }
       }
     }
@@ -212,10 +221,10 @@ __global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const GroupedArgs
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < MT; ++i) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int m = wm * 64 + i * 16 + (lane >> 2) + half * 8;
+      const int m = wm * MT * 16 + i * 16 + (lane >> 2) + half * 8;
       if (m >= rows) continue;
       const int r = row0 + m;
       const long long crow = p.rows_out ? p.rows_out[r] : r;
@@ -225,8 +234,8 @@ __global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const GroupedArgs
         f *= 1.f / (1.f + expf(-gv));
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2;
+      for (int j = 0; j < NT; ++j) {
+        const int n = n0 + wn * NT * 8 + j * 8 + (lane & 3) * 2;
         if (n >= p.N) continue;
         float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
         if (EPI == GEPI_RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
@@ -251,13 +260,16 @@ static inline bool mma_ok(const GroupedArgs& p) {
          !((uintptr_t)p.B & 15);
 }
 
+// grid: the caller's (column tiles and row tiles counted with C's sizes)
+template <typename C>
 static int launch_mma(int epi, const GroupedArgs& p, dim3 grid, cudaStream_t s) {
-#define GO(E)                                                                                        \
-  do {                                                                                               \
-    static bool done[64] = {};                                                                       \
-    const int rc = allow_dynamic_smem(grouped_gemm_mma_kernel<E>, MMA_SMEM, done);                   \
-    if (rc) return rc;                                                                               \
-    return launch_ex(grouped_gemm_mma_kernel<E>, grid, dim3(256), (size_t)MMA_SMEM, s, 1, p);        \
+  constexpr int SMEM = mma_smem<C>();
+#define GO(E)                                                                                          \
+  do {                                                                                                 \
+    static bool done[64] = {};                                                                         \
+    const int rc = allow_dynamic_smem(grouped_gemm_mma_kernel<E, C>, SMEM, done);                      \
+    if (rc) return rc;                                                                                 \
+    return launch_ex(grouped_gemm_mma_kernel<E, C>, grid, dim3(C::WM * C::WN * 32), (size_t)SMEM, s, 1, p); \
   } while (0)
   switch (epi) {
     case GEPI_STORE: GO(GEPI_STORE);
@@ -290,17 +302,21 @@ RLLM_API int rllm_grouped_gemm_uniform(int dt, int epi, const void* A, long long
   if ((T + BM - 1) / BM > 65535 || G > 65535) return ERR_TOO_LARGE;
   GroupedArgs p = {A, lda, a_gs, B, b_gs, C, ldc, c_gs, T, N, K, nullptr, nullptr, nullptr, nullptr, nullptr, gate, gate_ld};
   dim3 grid((N + BN - 1) / BN, (T + BM - 1) / BM, G);
-  if (dt == DT_BF16 && mma_ok(p) && (T + MB - 1) / MB <= 65535)
-    return launch_mma(epi, p, dim3((N + MN - 1) / MN, (T + MB - 1) / MB, G), (cudaStream_t)stream);
+  if (dt == DT_BF16 && mma_ok(p) && T <= FewTile::BM)
+    return launch_mma<FewTile>(epi, p, dim3((N + FewTile::BN - 1) / FewTile::BN, 1, G), (cudaStream_t)stream);
+  if (dt == DT_BF16 && mma_ok(p) && (T + LongTile::BM - 1) / LongTile::BM <= 65535)
+    return launch_mma<LongTile>(epi, p, dim3((N + LongTile::BN - 1) / LongTile::BN, (T + LongTile::BM - 1) / LongTile::BM, G),
+                                (cudaStream_t)stream);
   if (dt == DT_F32) return launch<float>(epi, p, grid, (cudaStream_t)stream);
   if (dt == DT_BF16) return launch<bf16>(epi, p, grid, (cudaStream_t)stream);
   return ERR_BAD_DTYPE;
 }
 
-// Rows a tile of the plan may have for a problem of this type and shape: the tile of the kernel that will
-// take it (the plan has to be made with it).
-RLLM_API int rllm_grouped_gemm_tile_rows(int dt, long long lda, int K) {
-  return (dt == DT_BF16 && K % 8 == 0 && lda % 8 == 0) ? MB : BM;
+// Rows a tile of the plan may have for a ragged problem of this type, shape and number of sorted rows: the tile
+// of the kernel that will take it (the plan has to be made with it). Few rows (decoding): tiles of 32.
+RLLM_API int rllm_grouped_gemm_tile_rows(int dt, long long lda, int K, int n_rows) {
+  if (!(dt == DT_BF16 && K % 8 == 0 && lda % 8 == 0)) return BM;
+  return n_rows <= 1024 ? FewTile::BM : LongTile::BM;
 }
 
 // Ragged problems: the tile table (`tiles`, `n_tiles`) comes from rllm_moe_plan, made with tiles of
@@ -314,8 +330,10 @@ RLLM_API int rllm_grouped_gemm_ragged(int dt, int epi, const void* A, long long 
   if (max_tiles > 65535) return ERR_TOO_LARGE;
   GroupedArgs p = {A, lda, 0, B, b_gs, C, ldc, 0, 0, N, K, tiles, n_tiles, rows_in, rows_out, row_scale, nullptr, 0};
   dim3 grid((N + BN - 1) / BN, max_tiles, 1);
-  if (dt == DT_BF16 && tile_rows == MB && mma_ok(p))
-    return launch_mma(epi, p, dim3((N + MN - 1) / MN, max_tiles, 1), (cudaStream_t)stream);
+  if (dt == DT_BF16 && tile_rows == LongTile::BM && mma_ok(p))
+    return launch_mma<LongTile>(epi, p, dim3((N + LongTile::BN - 1) / LongTile::BN, max_tiles, 1), (cudaStream_t)stream);
+  if (dt == DT_BF16 && tile_rows == FewTile::BM && mma_ok(p))
+    return launch_mma<FewTile>(epi, p, dim3((N + FewTile::BN - 1) / FewTile::BN, max_tiles, 1), (cudaStream_t)stream);
   if (tile_rows != BM) return ERR_BAD_SIZE;                          // the plan was made for the other kernel
   if (dt == DT_F32) return launch<float>(epi, p, grid, (cudaStream_t)stream);
   if (dt == DT_BF16) return launch<bf16>(epi, p, grid, (cudaStream_t)stream);

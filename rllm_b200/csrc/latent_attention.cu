@@ -224,6 +224,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
   bf16* ks = qs + QROWS * ld;                                        // [2][32][ld]
   float* ss = reinterpret_cast<float*>(ks + 2 * KT * ld);            // [64][33]
   __shared__ int key_ok[2][KT];
+  __shared__ int krow[KT];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = warp >> 1, half = warp & 1;                         // 16 rows each, two halves
   const int tok0 = cu_q[seq], ntok = cu_q[seq + 1] - tok0;
@@ -246,16 +247,28 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
     return;
   }
 
+  // where the next tile's keys lie: one lane a key looks its page up (row of the cache, -1: no such key),
+  // before the barrier that lets all warps copy the tile
+  auto find_keys = [&](int it) {
+    if (tid < KT) {
+      const int kj = key_first + it * KT + tid;
+      const int page = kj <= pos_hi ? bt[kj / page_size] : -1;
+      krow[tid] = page >= 0 ? page * page_size + kj % page_size : -1;
+    }
+  };
+  // a warp copies four keys of the tile, its lanes the 16-byte pieces of a row
   auto load_keys = [&](int it) {
     bf16* dst = ks + ((it - it0) & 1) * KT * ld;
-    for (int c = tid; c < KT * cpr; c += 256) {
-      const int j = c / cpr, piece = c % cpr;
-      const int kj = key_first + it * KT + j;
-      const int page = kj <= pos_hi ? bt[kj / page_size] : -1;
-      if (piece == 0) key_ok[(it - it0) & 1][j] = page >= 0;
-      const bool in = page >= 0 && piece * 8 < dk;
-      cp_async16(dst + j * ld + piece * 8,
-                 cache + (in ? ((long long)page * page_size + kj % page_size) * dk + piece * 8 : 0), in ? 16 : 0);
+#pragma unroll
+    for (int i = 0; i < KT / 8; ++i) {
+      const int j = warp + i * 8;
+      const int row = krow[j];
+      if (lane == 0) key_ok[(it - it0) & 1][j] = row >= 0;
+      const bf16* src = cache + (long long)(row < 0 ? 0 : row) * dk;
+      for (int piece = lane; piece < cpr; piece += 32) {
+        const bool in = row >= 0 && piece * 8 < dk;
+        cp_async16(dst + j * ld + piece * 8, src + (in ? piece * 8 : 0), in ? 16 : 0);
+      }
     }
   };
   // the queries, once (rows beyond the sequence's: zeros)
@@ -264,6 +277,8 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
     const bool in = r < nrows && piece * 8 < dk;
     cp_async16(qs + r * ld + piece * 8, qfull + (in ? ((long long)tok0 * H + row_first + r) * dk + piece * 8 : 0), in ? 16 : 0);
   }
+  find_keys(it0);
+  __syncthreads();
   load_keys(it0);
   asm volatile("cp.async.commit_group;" ::: "memory");
 
@@ -280,6 +295,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
   const int dk16 = (dk + 15) / 16;
 
   for (int it = it0; it < it1; ++it) {
+    if (it + 1 < it1) find_keys(it + 1);                             // krow was last read before the barrier before
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                                                 // tile `it` has landed; tile it - 1 is used up
     if (it + 1 < it1) load_keys(it + 1);
@@ -289,6 +305,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
     if (rg_live) {
       // scores of this warp's 16 rows against its 16 keys
       float sc[2][4] = {};
+#pragma unroll 2
       for (int kk = 0; kk < dk16; ++kk) {
         unsigned a[4], b[4];
         ldmatrix4(a, qs + (rg * 16 + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
@@ -378,17 +395,196 @@ latent_attention_mma_kernel(const bf16* __restrict__ qfull, const bf16* __restri
   }
 }
 
-// The splits' parts of every row, merged in split order: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
-__global__ void __launch_bounds__(256)
-latent_merge_kernel(const float* __restrict__ pacc, const float* __restrict__ pml, bf16* __restrict__ out,
-                    const int* __restrict__ cu_q, int num_seqs, int H, int rank, int splits) {
+// The few-rows shape of the kernel above (steps that bring a token or two per sequence): 16 rows a CTA, so that the
+// heads of one decoded token are a row tile by themselves; keys 64 at a time through two buffers. All eight warps
+// work on the one row tile: for the scores each takes 8 of the 64 keys, then every warp runs the float softmax
+// update of the 16 rows (the same numbers in each) and multiplies the weights with its eighth of the value columns.
+// rank a multiple of 128 (NW = rank / 64 column tiles of 8 a warp).
+constexpr int FROWS = 16, FKT = 64;
+
+template <int NW>
+__global__ void __launch_bounds__(256, 1)
+latent_attention_few_kernel(const bf16* __restrict__ qfull, const bf16* __restrict__ cache, bf16* __restrict__ out,
+                            const int* __restrict__ cu_q, const int* __restrict__ positions,
+                            const int* __restrict__ block_table, int bt_stride, int num_seqs, int H, int rank, int dk,
+                            int ld, int page_size, float scale, int window, int splits, float* __restrict__ pacc,
+                            float* __restrict__ pml) {
   pdl_launch();
   pdl_wait();
   int seq = -1, tile = 0;
   {
     int at = 0;
     for (int s = 0; s < num_seqs; ++s) {
-      const int n = ((cu_q[s + 1] - cu_q[s]) * H + QROWS - 1) / QROWS;
+      const int n = ((cu_q[s + 1] - cu_q[s]) * H + FROWS - 1) / FROWS;
+      if ((int)blockIdx.x < at + n) { seq = s; tile = blockIdx.x - at; break; }
+      at += n;
+    }
+  }
+  if (seq < 0) return;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                      // [16][ld]
+  bf16* ks = qs + FROWS * ld;                                        // [2][64][ld]
+  float* ss = reinterpret_cast<float*>(ks + 2 * FKT * ld);           // [16][65]
+  __shared__ int key_ok[2][FKT];
+  __shared__ int krow[FKT];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tok0 = cu_q[seq], ntok = cu_q[seq + 1] - tok0;
+  const int row_first = tile * FROWS, nrows = min(FROWS, ntok * H - row_first);
+  const int t_lo = tok0 + row_first / H, t_hi = tok0 + (row_first + nrows - 1) / H;
+  const int pos_lo = positions[t_lo], pos_hi = positions[t_hi];
+  const int key_first = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
+  const int ntiles = (pos_hi - key_first) / FKT + 1;
+  const int per_split = (ntiles + splits - 1) / splits;
+  const int it0 = blockIdx.y * per_split, it1 = min(ntiles, it0 + per_split);
+  const int* bt = block_table + (long long)seq * bt_stride;
+  const int cpr = (ld - 8) / 8;
+  const long long pb = ((long long)blockIdx.x * splits + blockIdx.y) * FROWS;
+  if (it0 >= it1) {
+    if (tid < FROWS) { pml[(pb + tid) * 2] = -INFINITY; pml[(pb + tid) * 2 + 1] = 0.f; }
+    return;
+  }
+  auto find_keys = [&](int it) {
+    if (tid < FKT) {
+      const int kj = key_first + it * FKT + tid;
+      const int page = kj <= pos_hi ? bt[kj / page_size] : -1;
+      krow[tid] = page >= 0 ? page * page_size + kj % page_size : -1;
+    }
+  };
+  auto load_keys = [&](int it) {
+    bf16* dst = ks + ((it - it0) & 1) * FKT * ld;
+#pragma unroll
+    for (int i = 0; i < FKT / 8; ++i) {
+      const int j = warp + i * 8;
+      const int row = krow[j];
+      if (lane == 0) key_ok[(it - it0) & 1][j] = row >= 0;
+      const bf16* src = cache + (long long)(row < 0 ? 0 : row) * dk;
+      for (int piece = lane; piece < cpr; piece += 32) {
+        const bool in = row >= 0 && piece * 8 < dk;
+        cp_async16(dst + j * ld + piece * 8, src + (in ? piece * 8 : 0), in ? 16 : 0);
+      }
+    }
+  };
+  for (int c = tid; c < FROWS * cpr; c += 256) {
+    const int r = c / cpr, piece = c % cpr;
+    const bool in = r < nrows && piece * 8 < dk;
+    cp_async16(qs + r * ld + piece * 8, qfull + (in ? ((long long)tok0 * H + row_first + r) * dk + piece * 8 : 0), in ? 16 : 0);
+  }
+  find_keys(it0);
+  __syncthreads();
+  load_keys(it0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  const int r0 = lane >> 2, r1 = r0 + 8;
+  int pos0 = -1, pos1 = -1, lo0 = 0, lo1 = 0;
+  if (r0 < nrows) { pos0 = positions[tok0 + (row_first + r0) / H]; lo0 = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0; }
+  if (r1 < nrows) { pos1 = positions[tok0 + (row_first + r1) / H]; lo1 = (window > 0 && pos1 - window + 1 > 0) ? pos1 - window + 1 : 0; }
+  float acc[NW][4];
+#pragma unroll
+  for (int n = 0; n < NW; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int dk16 = (dk + 15) / 16;
+
+  for (int it = it0; it < it1; ++it) {
+    if (it + 1 < it1) find_keys(it + 1);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (it + 1 < it1) load_keys(it + 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const bf16* kt = ks + ((it - it0) & 1) * FKT * ld;
+    const int kbase = key_first + it * FKT;
+    {
+      // scores of the 16 rows against this warp's 8 keys
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int kk = 0; kk < dk16; ++kk) {
+        unsigned a[4], b[4];
+        ldmatrix4(a, qs + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
+        // x4 over 8 keys x 32 of K would be two steps at once; keep to one step: lanes 16..31 repeat the addresses
+        ldmatrix4(b, kt + (warp * 8 + (lane & 7)) * ld + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma16816(sc, a, b[0], b[1]);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = warp * 8 + (lane & 3) * 2 + (e & 1);
+        const int kj = kbase + col;
+        const bool top = e < 2;
+        const bool seen = key_ok[(it - it0) & 1][col] && (top ? (kj >= lo0 && kj <= pos0) : (kj >= lo1 && kj <= pos1));
+        ss[(top ? r0 : r1) * (FKT + 1) + col] = seen ? sc[e] * scale : -INFINITY;
+      }
+    }
+    __syncthreads();
+    {
+      float p0[16], p1[16];
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        const int col = (q >> 1) * 8 + (lane & 3) * 2 + (q & 1);
+        p0[q] = ss[r0 * (FKT + 1) + col]; p1[q] = ss[r1 * (FKT + 1) + col];
+        mx0 = fmaxf(mx0, p0[q]); mx1 = fmaxf(mx1, p1[q]);
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;
+      const float c0 = expf(m0 - b0), c1 = expf(m1 - b1);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < 16; ++q) { p0[q] = expf(p0[q] - b0); p1[q] = expf(p1[q] - b1); s0 += p0[q]; s1 += p1[q]; }
+      s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+      l0 = l0 * c0 + s0; l1 = l1 * c1 + s1; m0 = n0; m1 = n1;
+#pragma unroll
+      for (int n = 0; n < NW; ++n) { acc[n][0] *= c0; acc[n][1] *= c0; acc[n][2] *= c1; acc[n][3] *= c1; }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        unsigned a[4] = {pack_bf16(p0[kk * 4], p0[kk * 4 + 1]), pack_bf16(p1[kk * 4], p1[kk * 4 + 1]),
+                         pack_bf16(p0[kk * 4 + 2], p0[kk * 4 + 3]), pack_bf16(p1[kk * 4 + 2], p1[kk * 4 + 3])};
+#pragma unroll
+        for (int n = 0; n < NW; n += 2) {
+          unsigned b[4];
+          ldmatrix4t(b, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + warp * NW * 8 + n * 8 + (lane >> 4) * 8);
+          mma16816(acc[n], a, b[0], b[1]);
+          mma16816(acc[n + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (splits > 1) {
+    if (warp == 0 && (lane & 3) == 0) { pml[(pb + r0) * 2] = m0; pml[(pb + r0) * 2 + 1] = l0;
+                                        pml[(pb + r1) * 2] = m1; pml[(pb + r1) * 2 + 1] = l1; }
+#pragma unroll
+    for (int n = 0; n < NW; ++n) {
+      const int col = warp * NW * 8 + n * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(pacc + (pb + r0) * rank + col) = make_float2(acc[n][0], acc[n][1]);
+      *reinterpret_cast<float2*>(pacc + (pb + r1) * rank + col) = make_float2(acc[n][2], acc[n][3]);
+    }
+    return;
+  }
+  const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+  bf16* o0 = out + ((long long)tok0 * H + row_first + r0) * rank;
+  bf16* o1 = out + ((long long)tok0 * H + row_first + r1) * rank;
+#pragma unroll
+  for (int n = 0; n < NW; ++n) {
+    const int col = warp * NW * 8 + n * 8 + (lane & 3) * 2;
+    if (r0 < nrows) *reinterpret_cast<__nv_bfloat162*>(o0 + col) = __floats2bfloat162_rn(acc[n][0] * i0, acc[n][1] * i0);
+    if (r1 < nrows) *reinterpret_cast<__nv_bfloat162*>(o1 + col) = __floats2bfloat162_rn(acc[n][2] * i1, acc[n][3] * i1);
+  }
+}
+
+// The splits' parts of every row, merged in split order: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
+// grid.x: the row tiles (of `qrows` rows) as in the kernel that left the parts; grid.y: blocks of 32 columns; a
+// warp takes rows, its lanes the columns, all splits' values asked for at once.
+__global__ void __launch_bounds__(256)
+latent_merge_kernel(const float* __restrict__ pacc, const float* __restrict__ pml, bf16* __restrict__ out,
+                    const int* __restrict__ cu_q, int num_seqs, int H, int rank, int splits, int qrows) {
+  pdl_launch();
+  pdl_wait();
+  int seq = -1, tile = 0;
+  {
+    int at = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int n = ((cu_q[s + 1] - cu_q[s]) * H + qrows - 1) / qrows;
       if ((int)blockIdx.x < at + n) { seq = s; tile = blockIdx.x - at; break; }
       at += n;
     }
@@ -396,25 +592,26 @@ latent_merge_kernel(const float* __restrict__ pacc, const float* __restrict__ pm
   if (seq < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok0 = cu_q[seq], ntok = cu_q[seq + 1] - tok0;
-  const int row_first = tile * QROWS, nrows = min(QROWS, ntok * H - row_first);
+  const int row_first = tile * qrows, nrows = min(qrows, ntok * H - row_first);
+  const int col = blockIdx.y * 32 + lane;
   for (int r = warp; r < nrows; r += 8) {
-    const long long pb = (long long)blockIdx.x * splits * QROWS + r;
-    const float m = lane < splits ? pml[(pb + (long long)lane * QROWS) * 2] : -INFINITY;
-    const float l = lane < splits ? pml[(pb + (long long)lane * QROWS) * 2 + 1] : 0.f;
+    const long long pb = (long long)blockIdx.x * splits * qrows + r;
+    const float m = lane < splits ? pml[(pb + (long long)lane * qrows) * 2] : -INFINITY;
+    const float l = lane < splits ? pml[(pb + (long long)lane * qrows) * 2 + 1] : 0.f;
     const float M = warp_max(m);
     const float w = (m == -INFINITY) ? 0.f : expf(m - M);
     const float L = warp_sum(w * l);
     const float inv = L > 0.f ? 1.f / L : 0.f;
-    bf16* o = out + ((long long)tok0 * H + row_first + r) * rank;
-    for (int c0 = 0; c0 < rank; c0 += 32) {
-      const int col = c0 + lane;
-      float a = 0.f;
-      for (int s = 0; s < splits; ++s) {
-        const float ws = __shfl_sync(0xffffffffu, w, s);
-        if (ws != 0.f && col < rank) a = fmaf(ws, pacc[(pb + (long long)s * QROWS) * rank + col], a);
-      }
-      if (col < rank) o[col] = __float2bfloat16_rn(a * inv);
+    float v[32];
+#pragma unroll
+    for (int s = 0; s < 32; ++s) {
+      const float ws = __shfl_sync(0xffffffffu, w, s);
+      v[s] = (s < splits && ws != 0.f && col < rank) ? ws * pacc[(pb + (long long)s * qrows) * rank + col] : 0.f;
     }
+    float a = 0.f;
+#pragma unroll
+    for (int s = 0; s < 32; ++s) a += v[s];
+    if (col < rank) out[((long long)tok0 * H + row_first + r) * rank + col] = __float2bfloat16_rn(a * inv);
   }
 }
 
@@ -441,34 +638,61 @@ RLLM_API int rllm_latent_prepare(int dt, const void* proj, long long ld, int q_o
 
 // qfull [T, H, dk]; cache [pages * page_size, dk]; out [T, H, rank].
 // cu_q [num_seqs + 1] (row range of each sequence; null: the tensor-core kernel is not used), `tc` 0 forbids it.
-// splits > 1 (tensor-core kernel only): the keys of every row tile are dealt out to that many CTAs; pacc: float
-// [row tiles, splits, 64, rank], pml: float [row tiles, splits, 64, 2], row tiles = ceil(T * H / 64) + num_seqs.
+// splits > 1 (tensor-core kernels only): the keys of every row tile are dealt out to that many CTAs; pacc: float
+// [row tiles, splits, rows, rank], pml: float [row tiles, splits, rows, 2], rows = 64 a tile, or 16 with `few`
+// (the shape for steps of a token or two per sequence; taken when rank is a multiple of 128), row tiles =
+// ceil(T * H / rows) + num_seqs.
 RLLM_API int rllm_latent_attention(int dt, const void* qfull, const void* cache, void* out, const int* token_seq,
                                    const int* positions, const int* block_table, int bt_stride, int T, int H, int rank,
                                    int dk, int page_size, float scale, int window, const int* cu_q, int num_seqs,
-                                   int tc, int splits, float* pacc, float* pml, void* stream) {
+                                   int tc, int splits, int few, float* pacc, float* pml, void* stream) {
   if (T <= 0) return 0;
   if (H <= 0 || rank <= 0 || rank > MAX_RANK || dk < rank || page_size <= 0) return ERR_BAD_SIZE;
   if (tc && dt == DT_BF16 && cu_q && num_seqs > 0 && dk % 8 == 0 && rank % 16 == 0 && rank <= 512 &&
       !((uintptr_t)qfull & 15) && !((uintptr_t)cache & 15) && !((uintptr_t)out & 3)) {
+    if (splits < 1 || splits > 32 || (splits > 1 && (!pacc || !pml))) return ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (few && rank % 128 == 0) {
+      // 16 rows a CTA: steps of a token or two per sequence
+      const int nw = rank / 64;
+      const int ld = mma_row_pad(dk, nw * 4);                        // 8 warps x nw tiles of 8 columns = rank
+      const int smem = (FROWS + 2 * FKT) * ld * 2 + FROWS * (FKT + 1) * 4;
+      const long long blocks = ((long long)T * H + FROWS - 1) / FROWS + num_seqs;
+      if (smem <= 220 * 1024 && blocks <= 2147483647LL) {
+#define GO(NW)                                                                                                          \
+  do {                                                                                                                  \
+    static bool done[64] = {};                                                                                          \
+    const int rc = allow_dynamic_smem(latent_attention_few_kernel<NW>, 220 * 1024, done);                               \
+    if (rc) return rc;                                                                                                  \
+    const int rl = launch_ex(latent_attention_few_kernel<NW>, dim3((unsigned)blocks, splits), dim3(256), (size_t)smem,  \
+                             s, 1, (const bf16*)qfull, (const bf16*)cache, (bf16*)out, cu_q, positions, block_table,    \
+                             bt_stride, num_seqs, H, rank, dk, ld, page_size, scale, window, splits, pacc, pml);        \
+    if (rl || splits == 1) return rl;                                                                                   \
+    return launch_ex(latent_merge_kernel, dim3((unsigned)blocks, (rank + 31) / 32), dim3(256), 0, s, 1,                 \
+                     (const float*)pacc, (const float*)pml, (bf16*)out, cu_q, num_seqs, H, rank, splits, FROWS);        \
+  } while (0)
+        if (nw == 2) GO(2);
+        if (nw == 4) GO(4);
+        if (nw == 8) GO(8);
+#undef GO
+      }
+    }
     const int nh = rank <= 64 ? 4 : rank <= 128 ? 8 : rank <= 256 ? 16 : 32;
     const int ld = mma_row_pad(dk, nh);
     const int smem = (QROWS + 2 * KT) * ld * 2 + QROWS * (KT + 1) * 4;
     const long long blocks = ((long long)T * H + QROWS - 1) / QROWS + num_seqs;
-    if (splits < 1 || splits > 32 || (splits > 1 && (!pacc || !pml))) return ERR_BAD_SIZE;
     if (smem <= 220 * 1024 && blocks <= 2147483647LL) {
 #define GO(NH)                                                                                                          \
   do {                                                                                                                  \
     static bool done[64] = {};                                                                                          \
     const int rc = allow_dynamic_smem(latent_attention_mma_kernel<NH>, 220 * 1024, done);                               \
     if (rc) return rc;                                                                                                  \
-    const int rl = launch_ex(latent_attention_mma_kernel<NH>, dim3((unsigned)blocks, splits), dim3(256), (size_t)smem, \
-                             (cudaStream_t)stream, 1, (const bf16*)qfull, (const bf16*)cache, (bf16*)out, cu_q,         \
-                             positions, block_table, bt_stride, num_seqs, H, rank, dk, ld, page_size, scale, window,    \
-                             splits, pacc, pml);                                                                        \
+    const int rl = launch_ex(latent_attention_mma_kernel<NH>, dim3((unsigned)blocks, splits), dim3(256), (size_t)smem,  \
+                             s, 1, (const bf16*)qfull, (const bf16*)cache, (bf16*)out, cu_q, positions, block_table,    \
+                             bt_stride, num_seqs, H, rank, dk, ld, page_size, scale, window, splits, pacc, pml);        \
     if (rl || splits == 1) return rl;                                                                                   \
-    return launch_ex(latent_merge_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1,                \
-                     (const float*)pacc, (const float*)pml, (bf16*)out, cu_q, num_seqs, H, rank, splits);               \
+    return launch_ex(latent_merge_kernel, dim3((unsigned)blocks, (rank + 31) / 32), dim3(256), 0, s, 1,                 \
+                     (const float*)pacc, (const float*)pml, (bf16*)out, cu_q, num_seqs, H, rank, splits, QROWS);        \
   } while (0)
       if (nh == 4) GO(4);
       if (nh == 8) GO(8);

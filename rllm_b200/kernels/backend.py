@@ -197,10 +197,11 @@ class Backend:
         return self._mix.grouped_gemm_uniform(a, a_gs, w, out, c_gs,
                                               self._mix.GEPI_STORE_F32 if f32 else self._mix.GEPI_STORE, gate=gate)
 
-    def expert_tile_rows(self, x, w_up, w_down):
+    def expert_tile_rows(self, x, w_up, w_down, n_rows):
         """Rows per tile of a plan that the up and the down product of a routed feed-forward share."""
-        return min(self._mix.tile_rows(x.dtype, x.stride(0), w_up.shape[2]),
-                   self._mix.tile_rows(x.dtype, w_down.shape[2], w_down.shape[2]))
+        up = self._mix.tile_rows(x.dtype, x.stride(0), w_up.shape[2], n_rows)
+        down = self._mix.tile_rows(x.dtype, w_down.shape[2], w_down.shape[2], n_rows)
+        return up if up == down else 64         # one of them stays on the CUDA cores: both take its tiles
 
     def route(self, logits, top, groups=1, keep=1, renorm=False, tile_rows=64):
         """Router logits -> the plan of the experts' grouped products (all on the device)."""
@@ -226,16 +227,19 @@ class Backend:
 
     def latent_attention(self, qfull, cache, ctx, rank, scale, window):
         # Steps of few rows (decoding) have fewer row tiles than the GPU has SMs: the keys of a tile are then
-        # dealt out to several CTAs, at least four key tiles (128 keys) each. Everything this depends on is
-        # known when a decode graph is captured (rows, sequences, the bound of the key count).
+        # dealt out to several CTAs, at least four key tiles (128 keys) each; steps of a token or two per
+        # sequence take the kernel shape with 16 rows a CTA. Everything this depends on is known when a decode
+        # graph is captured (rows, sequences, the longest portion, the bound of the key count).
         T, H = qfull.shape[0], qfull.shape[1]
-        tiles = (T * H + 63) // 64 + ctx.num_seqs
+        few = ctx.max_q_len <= 2 and rank % 128 == 0
+        rows = 16 if few else 64
+        tiles = max(1, T * H // rows)               # row tiles the step has at least
         keys = min(window, ctx.max_kv_len) if window else ctx.max_kv_len
         splits = max(1, min(16, self.sm_count // tiles, keys // 128))
         return self._mix.latent_attention(qfull, cache.tensors["kv"], ctx.token_seq, ctx.positions,
                                           cache.block_table, rank, scale, window, cu_q=ctx.cu_q, num_seqs=ctx.num_seqs,
                                           tensor_cores=self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1",
-                                          splits=splits)
+                                          splits=splits, few=few)
 
     def gla_decay(self, z, bias, tau):
         return self._mix.gla_decay(z, bias, tau)

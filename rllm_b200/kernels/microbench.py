@@ -206,7 +206,7 @@ def cmd_experts(a) -> None:
     for T in a.tokens:
         x = torch.randn(T, W, device=DEV, dtype=torch.bfloat16)
         logits = torch.randn(T, E, device=DEV)
-        per_tile = min(mix.tile_rows(torch.bfloat16, W, W), mix.tile_rows(torch.bfloat16, F, F))
+        per_tile = mix.tile_rows(torch.bfloat16, W, W, T * top) if W % 8 == 0 and F % 8 == 0 else 64
         idx, wt = mix.moe_topk(logits, top, a.groups, a.keep)
         plan = mix.moe_plan(idx, wt, E, per_tile)
         act = torch.empty(T * top, F, device=DEV, dtype=torch.bfloat16)
@@ -240,13 +240,15 @@ def cmd_latent_attn(a) -> None:
         bt, pos, seq, cu, pages = _paged(batch, context, new, page)
         caches = [torch.randn(pages, page, dk, device=DEV, dtype=torch.bfloat16) for _ in range(a.copies)]
         q = torch.randn(batch * new, H, dk, device=DEV, dtype=torch.bfloat16)
-        tiles = (batch * new * H + 63) // 64 + batch
+        few = new <= 2 and rank % 128 == 0 and not a.wide
+        rows = 16 if few else 64
+        tiles = max(1, batch * new * H // rows)
         keys = min(a.window, context) if a.window else context
         splits = a.splits or max(1, min(16, torch.cuda.get_device_properties(0).multi_processor_count // tiles, keys // 128))
         seen = sum(min(p + 1, a.window or p + 1) for p in range(context - new, context)) * batch
         run([lambda c=c: mix.latent_attention(q, c, seq, pos, bt, rank, dk ** -0.5, a.window or None, cu_q=cu,
-                                              num_seqs=batch, tensor_cores=not a.simt, splits=splits) for c in caches],
-            a.plain, f"latent attention {batch} x {new} tokens, context {context}, {H} heads, splits {splits}",
+                                              num_seqs=batch, tensor_cores=not a.simt, splits=splits, few=few) for c in caches],
+            a.plain, f"latent attention {batch} x {new} tokens, context {context}, {H} heads, splits {splits}, rows a CTA {rows}",
             batch * min(context, keys + new) * dk * 2 + 2 * q.numel() * 2, 2.0 * H * (dk + rank) * seen)
 
 
@@ -294,6 +296,7 @@ def main(argv=None) -> int:
                  ("splits", 0)):
         p.add_argument("--" + k, type=int, default=v)
     p.add_argument("--simt", action="store_true", help="the CUDA-core kernel")
+    p.add_argument("--wide", action="store_true", help="64 rows a CTA also for single tokens")
     p = sub.add_parser("gla")
     p.add_argument("--plain", type=int, default=0)
     p.add_argument("--copies", type=int, default=8)

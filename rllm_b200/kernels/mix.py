@@ -22,7 +22,7 @@ ops.register_signatures("mix", {
                                   _P, _LL, _P],
     "rllm_grouped_gemm_ragged": [c_int, c_int, _P, _LL, _P, _LL, _P, _LL, c_int, c_int, _P, _P, c_int, c_int, _P, _P, _P,
                                  _P],
-    "rllm_grouped_gemm_tile_rows": [c_int, _LL, c_int],
+    "rllm_grouped_gemm_tile_rows": [c_int, _LL, c_int, c_int],
     "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
     "rllm_moe_plan": [_P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "rllm_rmsnorm_add": [_P, c_int, _P, _P, c_int, c_int, c_float, _P],
@@ -30,7 +30,7 @@ ops.register_signatures("mix", {
     "rllm_latent_prepare": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_float, _P,
                             _P, _P, _P, _P],
     "rllm_latent_attention": [c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                              c_int, _P, c_int, c_int, c_int, _P, _P, _P],
+                              c_int, _P, c_int, c_int, c_int, c_int, _P, _P, _P],
     "rllm_gla_decay": [_P, _P, c_int, c_int, c_float, _P],
     "rllm_gla_scan": [c_int, _P, _LL, c_int, c_int, c_int, _P, c_float, c_int, c_int, c_int, c_int, c_int, _P, _P, _P,
                       _P, c_int, _P, _P, _P],
@@ -114,11 +114,11 @@ class RoutePlan:
     __slots__ = ("rows_tok", "rows_dest", "rows_scale", "tiles", "n_tiles", "max_tiles", "n_rows", "tile_rows")
 
 
-def tile_rows(dtype: torch.dtype, lda: int, K: int) -> int:
+def tile_rows(dtype: torch.dtype, lda: int, K: int, n_rows: int = 1 << 30) -> int:
     """Rows a plan's tile may have for a ragged product whose input has dtype `dtype`, row stride `lda` and
-    depth K: 128 where the tensor-core kernel takes it, 64 for the CUDA-core one. The products that share a
-    plan must agree (take the smallest)."""
-    return _fn("mix", "rllm_grouped_gemm_tile_rows")(ops._DT[dtype], int(lda), int(K))
+    depth K, over `n_rows` sorted rows: 128 where the tensor-core kernel takes it (32 for short lists), 64
+    for the CUDA-core one. The products that share a plan must agree (take the smallest)."""
+    return _fn("mix", "rllm_grouped_gemm_tile_rows")(ops._DT[dtype], int(lda), int(K), int(min(n_rows, 1 << 30)))
 
 
 def moe_topk(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
@@ -204,11 +204,12 @@ def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: int, heads: int, dim
 def latent_attention(qfull: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                      block_table: torch.Tensor, rank: int, scale: float, window: int | None,
                      cu_q: torch.Tensor | None = None, num_seqs: int = 0, tensor_cores: bool = True,
-                     splits: int = 1) -> torch.Tensor:
+                     splits: int = 1, few: bool = False) -> torch.Tensor:
     """qfull [T, heads, dk]; cache [pages, page, dk] -> [T, heads, rank] of qfull's dtype. With `cu_q`
     (int32 [num_seqs + 1], the row range of each sequence) bfloat16 problems of fitting sizes run on the
     tensor cores (`tensor_cores` False: never); `splits` > 1 there deals a row tile's keys out to that many
-    CTAs and merges their parts (steps of few rows)."""
+    CTAs and merges their parts (steps of few rows); `few` asks for the kernel shape with 16 rows a CTA (a
+    token or two per sequence; taken where the rank is a multiple of 128)."""
     _cuda(qfull, "qfull"); _cuda(cache, "cache")
     T, H, dk = qfull.shape
     if not qfull.is_contiguous() or not cache.is_contiguous() or cache.dtype != qfull.dtype or cache.dim() != 3 \
@@ -223,17 +224,19 @@ def latent_attention(qfull: torch.Tensor, cache: torch.Tensor, token_seq: torch.
     out = torch.empty((T, H, rank), dtype=qfull.dtype, device=qfull.device)
     pacc = pml = None
     splits = max(1, min(int(splits), 32))
+    few = bool(few) and rank % 128 == 0
     if splits > 1 and cu_q is not None:
-        tiles = (T * H + 63) // 64 + num_seqs
-        pacc = torch.empty((tiles, splits, 64, rank), dtype=torch.float32, device=qfull.device)
-        pml = torch.empty((tiles, splits, 64, 2), dtype=torch.float32, device=qfull.device)
+        rows = 16 if few else 64
+        tiles = (T * H + rows - 1) // rows + num_seqs
+        pacc = torch.empty((tiles, splits, rows, rank), dtype=torch.float32, device=qfull.device)
+        pml = torch.empty((tiles, splits, rows, 2), dtype=torch.float32, device=qfull.device)
     else:
         splits = 1
     _check(_fn("mix", "rllm_latent_attention")(
         _dt(qfull, "qfull"), qfull.data_ptr(), cache.data_ptr(), out.data_ptr(), token_seq.data_ptr(),
         positions.data_ptr(), block_table.data_ptr(), block_table.stride(0), T, H, rank, dk, cache.shape[1],
-        float(scale), int(window or 0), _ptr(cu_q), int(num_seqs), int(bool(tensor_cores)), splits, _ptr(pacc),
-        _ptr(pml), _stream()), "latent_attention", 2 if splits > 1 else 1)
+        float(scale), int(window or 0), _ptr(cu_q), int(num_seqs), int(bool(tensor_cores)), splits, int(few),
+        _ptr(pacc), _ptr(pml), _stream()), "latent_attention", 2 if splits > 1 else 1)
     return out
 
 

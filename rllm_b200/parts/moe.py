@@ -41,7 +41,7 @@ class RoutedExperts(Part):
         be = ctx.backend
         x = x.tensor() if hasattr(x, "tensor") else x
         _, _, plan = be.route(be.linear_f32(x, self.w_router), self.top, self.groups, self.keep, self.renorm,
-                              tile_rows=be.expert_tile_rows(x, self._up, self._down))
+                              tile_rows=be.expert_tile_rows(x, self._up, self._down, x.shape[0] * self.top))
         return be.experts_down(be.experts_up(x, self._up, plan, self.act), self._down, plan, x.shape[0], self.top)
 
 

@@ -150,8 +150,14 @@ def test_grouped_products(dtype, T, G, K, N, W, F):
     E, top = 5, 2
     x, up, down = rnd(T, W, seed=4).to(dt), rnd(E, F, W, seed=5, scale=0.3).to(dt), rnd(E, W, F, seed=6, scale=0.3).to(dt)
     gi, gw = mix.moe_topk(rnd(T, E, seed=7).to(DEV), top)
-    per_tile = min(mix.tile_rows(dt, W, W), mix.tile_rows(dt, F, F))
-    assert per_tile == (128 if dtype == "bfloat16" and W % 8 == 0 and F % 8 == 0 else 64)
+    aligned = dtype == "bfloat16" and W % 8 == 0 and F % 8 == 0
+    assert min(mix.tile_rows(dt, W, W), mix.tile_rows(dt, F, F)) == (128 if aligned else 64)
+    assert mix.tile_rows(dt, W, W, 100) == (32 if aligned else 64)
+    for per_tile in ((128, 32) if aligned else (64,)):        # the kernel's shape for long and for short row lists
+        check_ragged(mix, dt, dtype, T, E, top, W, F, x, up, down, gi, gw, per_tile)
+
+
+def check_ragged(mix, dt, dtype, T, E, top, W, F, x, up, down, gi, gw, per_tile):
     plan = mix.moe_plan(gi, gw, E, per_tile)
     act = torch.empty(T * top, F, dtype=dt, device=DEV)
     mix.grouped_gemm_ragged(x.to(DEV), up.to(DEV), plan, act, mix.GEPI_RELU2, gather=True)
@@ -253,20 +259,21 @@ def test_latent_attention_over_steps(dtype, m, page):
     assert rel(again, want_b) < tol
 
 
+@pytest.mark.parametrize("rank", [64, 128])
 @pytest.mark.parametrize("window", [None, 300])
-def test_latent_decoding_deals_the_keys_out_to_several_ctas(window):
+def test_latent_decoding_deals_the_keys_out_to_several_ctas(window, rank):
     """Single tokens of two sequences against 600 and 260 cached keys in bfloat16: the row tiles' keys are
     split over CTAs whose parts are merged; one far key (position 7) and one at the window's edge are made
     to win their scores."""
     from rllm_b200.parts import InterleavedRotary, LatentAttention
     W, dtype = 48, "bfloat16"
-    m = Z.latent(16, 16, 16, 24, 64, 0.2, 10000.0, 16, window)
+    m = Z.latent(16, 16, 16, 24, rank, 0.2, 10000.0, 16, window)
     w = latent_weights(W, m, seed=77)
     ha, hb = rnd(606, W, seed=1), rnd(266, W, seed=2)
     for p in (7, 606 - 300, 606 - 301):
         ha[p] *= 6.0
     want = {k: P.latent_attention(x.to(DT[dtype]).double(), as_stored(w, dtype), "x.", m, 1e-6) for k, x in (("a", ha), ("b", hb))}
-    part = LatentAttention(W, 16, 16, 16, 24, 64, 0.2, InterleavedRotary(16, 10000.0, 16), window=window, eps=1e-6)
+    part = LatentAttention(W, 16, 16, 16, 24, rank, 0.2, InterleavedRotary(16, 10000.0, 16), window=window, eps=1e-6)
     bind(part, w, dtype, "x.")
     da, db = ha.to(DT[dtype]).to(DEV), hb.to(DT[dtype]).to(DEV)
     hs = Harness(dtype, [part.cache_spec()], page_size=16, pages=64)
@@ -276,7 +283,8 @@ def test_latent_decoding_deals_the_keys_out_to_several_ctas(window):
     for i in range(6):
         def step(ctx, cache):
             T, H = 2, 16
-            tiles = (T * H + 63) // 64 + ctx.num_seqs
+            rows = 16 if rank % 128 == 0 else 64
+            tiles = max(1, T * H // rows)
             keys = min(window, ctx.max_kv_len) if window else ctx.max_kv_len
             seen.append(max(1, min(16, ctx.backend.sm_count // tiles, keys // 128)))
             return part.forward(torch.cat([da[600 + i: 601 + i], db[260 + i: 261 + i]]), ctx, cache)
