@@ -118,12 +118,12 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const GroupedArgs p) 
 }
 
 // ------------------------------------------------------------------------------------------ tensor cores
-// Two shapes of the kernel: LONG for tiles of up to 128 rows (prompt portions: 128 x 128 x 32, three stages,
+// Two shapes of the kernel: LONG for tiles of up to 128 rows (prompt portions: 128 x 128 x 64, three stages,
 // eight warps of 64 x 32), FEW for tiles of up to 32 rows (decoding: what counts is the weights' way through
 // the ring, so 256 contiguous bytes of a weight row per copy step, four stages, tiles of 64 weight rows so
 // that there are CTAs for every SM; four warps of 32 x 16).
-struct LongTile { static constexpr int BM = 128, BN = 128, BK = 32, ST = 3, WM = 2, WN = 4; };
-struct FewTile { static constexpr int BM = 32, BN = 64, BK = 128, ST = 4, WM = 1, WN = 4; };
+struct LongTile { static constexpr int BM = 128, BN = 128, BK = 64, ST = 3, WM = 2, WN = 4, CTAS = 2; };
+struct FewTile { static constexpr int BM = 32, BN = 64, BK = 128, ST = 4, WM = 1, WN = 4, CTAS = 2; };
 template <typename C> constexpr int mma_smem() { return C::ST * (C::BM + C::BN) * (C::BK + 8) * 2; }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
@@ -142,7 +142,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
 }
 
 template <int EPI, typename C>
-__global__ void __launch_bounds__(C::WM * C::WN * 32) grouped_gemm_mma_kernel(const GroupedArgs p) {
+__global__ void __launch_bounds__(C::WM * C::WN * 32, C::CTAS) grouped_gemm_mma_kernel(const GroupedArgs p) {
   pdl_launch();
   pdl_wait();
   constexpr int BM_ = C::BM, BN_ = C::BN, BK_ = C::BK, ST_ = C::ST, THREADS = C::WM * C::WN * 32;
@@ -201,19 +201,26 @@ __global__ void __launch_bounds__(C::WM * C::WN * 32) grouped_gemm_mma_kernel(co
     asm volatile("cp.async.commit_group;" ::: "memory");
     const bf16* as = As + (kb % ST_) * BM_ * LDS;
     const bf16* bs = Bs + (kb % ST_) * BN_ * LDS;
-#pragma unroll
-    for (int kk = 0; kk < BK_; kk += 16) {
-      unsigned bfrag[NT / 2][4];
+    // the fragments of the next 16 of K are asked for before the products of the current 16 are issued
+    unsigned bfrag[2][NT / 2][4], afrag[2][MT][4];
+    auto fetch = [&](int buf, int kk) {
 #pragma unroll
       for (int j = 0; j < NT / 2; ++j)
-        ldmatrix4(bfrag[j], bs + (wn * NT * 8 + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * LDS + kk + ((lane >> 3) & 1) * 8);
+        ldmatrix4(bfrag[buf][j], bs + (wn * NT * 8 + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * LDS + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+        if (i < mt_live) ldmatrix4(afrag[buf][i], as + (wm * MT * 16 + i * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8);
+    };
+    fetch(0, 0);
+#pragma unroll
+    for (int ks = 0; ks < BK_ / 16; ++ks) {
+      if (ks + 1 < BK_ / 16) fetch((ks + 1) & 1, (ks + 1) * 16);
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         if (i < mt_live) {
-          unsigned afrag[4];
-          ldmatrix4(afrag, as + (wm * MT * 16 + i * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8);
 #pragma unroll
-          for (int j = 0; j < NT; ++j) mma16816(acc[i][j], afrag, bfrag[j >> 1][(j & 1) * 2], bfrag[j >> 1][(j & 1) * 2 + 1]);
+          for (int j = 0; j < NT; ++j)
+            mma16816(acc[i][j], afrag[ks & 1][i], bfrag[ks & 1][j >> 1][(j & 1) * 2], bfrag[ks & 1][j >> 1][(j & 1) * 2 + 1]);
         }
       }
     }
@@ -267,6 +274,11 @@ static int launch_mma(int epi, const GroupedArgs& p, dim3 grid, cudaStream_t s) 
 #define GO(E)                                                                                          \
   do {                                                                                                 \
     static bool done[64] = {};                                                                         \
+    int dev = 0;                                                                                       \
+    cudaGetDevice(&dev);                                                                               \
+    if (dev >= 0 && dev < 64 && !done[dev]) /* once: as much of an SM as shared memory as there is */  \
+      cudaFuncSetAttribute(grouped_gemm_mma_kernel<E, C>, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                           (int)cudaSharedmemCarveoutMaxShared);                                       \
     const int rc = allow_dynamic_smem(grouped_gemm_mma_kernel<E, C>, SMEM, done);                      \
     if (rc) return rc;                                                                                 \
     return launch_ex(grouped_gemm_mma_kernel<E, C>, grid, dim3(C::WM * C::WN * 32), (size_t)SMEM, s, 1, p); \

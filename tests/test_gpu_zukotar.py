@@ -525,6 +525,26 @@ def test_greedy_generation_through_the_entry_point(dirs, name):
     llm.engine.cache.check()
 
 
+def test_ten_requests_decode_in_a_padded_graph(dirs):
+    """Ten requests decode side by side: their graph has twelve rows, two of them stand-ins without state slot,
+    pages or wanted logits, which must neither disturb the others nor touch a state."""
+    from rllm_b200.engine import Entry, load_engine
+    name = "ZA"
+    cfg, w = P.read_model_dir(dirs[name])
+    toks = {i: Z.random_prompt(5 + 3 * i + 9, 160, 300 + i) for i in range(10)}
+    want = {i: P.forward(cfg, w, t).numpy() for i, t in toks.items()}
+    eng = load_engine(dirs[name], dtype="float32", page_size=4, max_tokens=10 * 64, max_requests=10)
+    eng.step([Entry(i, t[:-9], []) for i, t in toks.items()])
+    got = {}
+    for k in range(9):
+        lg = eng.step([Entry(i, [t[len(t) - 9 + k]], [0]) for i, t in toks.items()]).float().cpu().numpy()
+        for row, (i, t) in enumerate(toks.items()):
+            got[(i, len(t) - 9 + k)] = lg[row]
+    eng.check()
+    assert eng.graph_steps == 9
+    check(got, {(i, p): want[i][p] for (i, p) in got}, 3e-5, "padded graph")
+
+
 def test_command_line_runs_the_design(dirs):
     import os, subprocess, sys
     name = "ZD"
