@@ -59,7 +59,7 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
                 float* __restrict__ chunk_decay) {
   pdl_launch();
   pdl_wait();
-  __shared__ float qs[CH][MAX_DIM], ks[CH][MAX_DIM], as[CH][MAX_DIM];
+  __shared__ __align__(16) float qs[CH][MAX_DIM], ks[CH][MAX_DIM], as[CH][MAX_DIM];
   __shared__ float vs[CH][32];
   __shared__ float part[CH][4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -72,6 +72,7 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
   const int kp = (dim + 3) / 4;                  // key channels of a warp
   const int kbase = warp * kp;
   const bool vok = v < vdim;
+  const bool vec = kp % 4 == 0 && dim % 4 == 0 && 4 * kp == dim;       // every warp has kp whole channels, in fours
   float S[KP], A[MODE == LOCAL ? KP : 1];
   // where this thread's share of a state lies: the request's slot, or the chunk's place in the scratch
   float* sp = (MODE == WHOLE ? state + ((long long)(slot < 0 ? 0 : slot) * H + h) * dim * vdim
@@ -88,7 +89,7 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
     for (int x = threadIdx.x; x < n * dim; x += 128) {
       const int cc = x / dim, k = x % dim;
       const TI* r = proj + (long long)(c0 + cc) * ld;
-      qs[cc][k] = to_f32(r[q_off + h * dim + k]) * qscale;
+      if (MODE != LOCAL) qs[cc][k] = to_f32(r[q_off + h * dim + k]) * qscale;
       ks[cc][k] = to_f32(r[k_off + h * dim + k]);
       as[cc][k] = alpha[(long long)(c0 + cc) * H * dim + h * dim + k];
     }
@@ -98,19 +99,44 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
       vs[cc][j] = vv < vdim ? to_f32(proj[(long long)(c0 + cc) * ld + v_off + h * vdim + vv]) : 0.f;
     }
     __syncthreads();
-    for (int cc = 0; cc < n; ++cc) {
-      const float val = vs[cc][lane];
-      float o = 0.f;
+    if (vec) {
+      // a warp's key channels are a multiple of 4: decays, keys and queries come four at a time
+      for (int cc = 0; cc < n; ++cc) {
+        const float val = vs[cc][lane];
+        const float4* a4 = reinterpret_cast<const float4*>(&as[cc][kbase]);
+        const float4* k4 = reinterpret_cast<const float4*>(&ks[cc][kbase]);
+        const float4* q4 = reinterpret_cast<const float4*>(&qs[cc][kbase]);
+        float o = 0.f;
 #pragma unroll
-      for (int i = 0; i < KP; ++i) {
-        const int k = kbase + i;
-        if (i < kp && k < dim) {
-          S[i] = fmaf(as[cc][k], S[i], ks[cc][k] * val);
-          if (MODE == LOCAL) A[i] *= as[cc][k];
-          else o = fmaf(S[i], qs[cc][k], o);
+        for (int i = 0; i < KP; i += 4) {
+          if (i < kp) {
+            const float4 a = a4[i >> 2], kk = k4[i >> 2];
+            S[i] = fmaf(a.x, S[i], kk.x * val); S[i + 1] = fmaf(a.y, S[i + 1], kk.y * val);
+            S[i + 2] = fmaf(a.z, S[i + 2], kk.z * val); S[i + 3] = fmaf(a.w, S[i + 3], kk.w * val);
+            if (MODE == LOCAL) { A[i] *= a.x; A[i + 1] *= a.y; A[i + 2] *= a.z; A[i + 3] *= a.w; }
+            else {
+              const float4 q = q4[i >> 2];
+              o = fmaf(S[i], q.x, o); o = fmaf(S[i + 1], q.y, o); o = fmaf(S[i + 2], q.z, o); o = fmaf(S[i + 3], q.w, o);
+            }
+          }
         }
+        if (MODE != LOCAL) part[cc][warp][lane] = o;
       }
-      if (MODE != LOCAL) part[cc][warp][lane] = o;
+    } else {
+      for (int cc = 0; cc < n; ++cc) {
+        const float val = vs[cc][lane];
+        float o = 0.f;
+#pragma unroll
+        for (int i = 0; i < KP; ++i) {
+          const int k = kbase + i;
+          if (i < kp && k < dim) {
+            S[i] = fmaf(as[cc][k], S[i], ks[cc][k] * val);
+            if (MODE == LOCAL) A[i] *= as[cc][k];
+            else o = fmaf(S[i], qs[cc][k], o);
+          }
+        }
+        if (MODE != LOCAL) part[cc][warp][lane] = o;
+      }
     }
     __syncthreads();
     if (MODE != LOCAL)
@@ -150,11 +176,16 @@ __global__ void gla_carry_kernel(const int* __restrict__ cu_q, const int* __rest
   float* sp = state + ((long long)(slot < 0 ? 0 : slot) * H + h) * dim * vdim + e;
   float S = slot >= 0 ? *sp : 0.f;
   const int k = e / vdim;
+  float* b = chunk_state + ((long long)base * H + h) * dim * vdim + e;
+  const float* d = chunk_decay + ((long long)base * H + h) * dim + k;
+  const long long bstep = (long long)H * dim * vdim, dstep = (long long)H * dim;
+  float bc = n > 0 ? *b : 0.f, dc = n > 0 ? *d : 0.f;
   for (int c = 0; c < n; ++c) {
-    float* b = chunk_state + ((long long)(base + c) * H + h) * dim * vdim + e;
-    const float next = fmaf(chunk_decay[((long long)(base + c) * H + h) * dim + k], S, *b);
+    float bn = 0.f, dn = 0.f;
+    if (c + 1 < n) { bn = b[bstep]; dn = d[dstep]; }                   // the next chunk's, asked for ahead
     *b = S;
-    S = next;
+    S = fmaf(dc, S, bc);
+    bc = bn; dc = dn; b += bstep; d += dstep;
   }
   if (slot >= 0) *sp = S;
 }
