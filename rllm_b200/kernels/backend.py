@@ -208,18 +208,31 @@ class Backend:
         idx, wt = self._mix.moe_topk(logits, top, groups, keep, renorm)
         return idx, wt, self._mix.moe_plan(idx, wt, logits.shape[1], tile_rows)
 
+    def _tc_experts(self, a, w, plan):
+        """Long row lists in bfloat16 go to the tcgen05 grouped product (RLLM_B200_NO_TC_EXPERTS=1: never)."""
+        return self._sm100 is not None and plan.tile_rows == 128 and a.dtype == torch.bfloat16 \
+            and os.environ.get("RLLM_B200_NO_TC_EXPERTS") != "1" and self._mix.tc_supported(a.stride(0), w.shape[1], w.shape[2])
+
     def experts_up(self, x, w_up, plan, act="relu2"):
         """act(x[token of row] W_up[expert of row]^T) for every sorted row of the plan."""
         if act != "relu2":
             raise ops.KernelError(f"expert activation {act!r} has no kernel")
         out = torch.empty((plan.n_rows, w_up.shape[1]), dtype=x.dtype, device=x.device)
+        if self._tc_experts(x, w_up, plan):
+            rows = self._mix.gather_rows_bf16(x, plan.rows_tok)       # the sorted rows as a matrix of their own: TMA boxes
+            return self._mix.grouped_gemm_tc(rows, w_up, plan, out, self._mix.GEPI_RELU2,
+                                             err=self._sm100.init(self.device).err)
         return self._mix.grouped_gemm_ragged(x, w_up, plan, out, self._mix.GEPI_RELU2, gather=True)
 
     def experts_down(self, a, w_down, plan, T, top):
         """weight of row * (a[row] W_down[expert of row]^T), stored at the row's (token, slot): float
         [T, top, width], every place written exactly once."""
         out = torch.empty((T * top, w_down.shape[1]), dtype=torch.float32, device=a.device)
-        self._mix.grouped_gemm_ragged(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=True)
+        if self._tc_experts(a, w_down, plan):
+            self._mix.grouped_gemm_tc(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=True,
+                                      err=self._sm100.init(self.device).err)
+        else:
+            self._mix.grouped_gemm_ragged(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=True)
         return out.view(T, top, w_down.shape[1])
 
     def latent_prepare(self, *a, **k):

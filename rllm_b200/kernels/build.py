@@ -31,7 +31,7 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 LIBRARIES: dict[str, list[str]] = {
     "simt": ["simt_basic.cu", "simt_gemm.cu", "simt_attention.cu", "sampling.cu"],
     "sm100": ["tc_gemm.cu", "stream_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu", "wait_probe.cu"],
-    "mix": ["grouped_gemm.cu", "moe_route.cu", "latent_attention.cu", "gla.cu"],
+    "mix": ["grouped_gemm.cu", "grouped_gemm_tc.cu", "moe_route.cu", "latent_attention.cu", "gla.cu"],
     "host": ["host_runtime.cpp"],          # no CUDA: the cache manager's bookkeeping and metadata writer
 }
 

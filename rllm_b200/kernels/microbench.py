@@ -214,11 +214,23 @@ def cmd_experts(a) -> None:
         used = int(torch.unique(idx).numel())
         run([lambda: (mix.moe_topk(logits, top, a.groups, a.keep), mix.moe_plan(idx, wt, E, per_tile))], a.plain,
             f"route+plan T={T}")
-        run([lambda u=u: mix.grouped_gemm_ragged(x, u, plan, act, mix.GEPI_RELU2, gather=True) for u in ups], a.plain,
-            f"experts_up T={T} ({used} experts used)", used * F * W * 2 + T * top * (F + W) * 2, 2.0 * T * top * F * W)
-        run([lambda d=d: mix.grouped_gemm_ragged(act, d, plan, out, mix.GEPI_STORE_F32, scatter=True, scale=True)
-             for d in downs], a.plain, f"experts_down T={T}", used * F * W * 2 + T * top * (2 * F + 4 * W),
-            2.0 * T * top * F * W)
+        tc = per_tile == 128 and not a.mma and mix.tc_supported(W, F, W) and mix.tc_supported(F, W, F)
+        if tc:
+            err = sm100.init(DEV).err
+            run([lambda: mix.gather_rows_bf16(x, plan.rows_tok)], a.plain, f"gather rows T={T}", 2 * T * top * W * 2)
+            rows = mix.gather_rows_bf16(x, plan.rows_tok)
+            up_fn = lambda u: mix.grouped_gemm_tc(rows, u, plan, act, mix.GEPI_RELU2, err=err)
+            down_fn = lambda d: mix.grouped_gemm_tc(act, d, plan, out, mix.GEPI_STORE_F32, scatter=True, scale=True, err=err)
+        else:
+            up_fn = lambda u: mix.grouped_gemm_ragged(x, u, plan, act, mix.GEPI_RELU2, gather=True)
+            down_fn = lambda d: mix.grouped_gemm_ragged(act, d, plan, out, mix.GEPI_STORE_F32, scatter=True, scale=True)
+        kind = "tcgen05" if tc else "mma.sync"
+        run([lambda u=u: up_fn(u) for u in ups], a.plain,
+            f"experts_up T={T} ({used} experts used, {kind})", used * F * W * 2 + T * top * (F + W) * 2, 2.0 * T * top * F * W)
+        run([lambda d=d: down_fn(d) for d in downs], a.plain, f"experts_down T={T} ({kind})",
+            used * F * W * 2 + T * top * (2 * F + 4 * W), 2.0 * T * top * F * W)
+        if tc:
+            sm100.check_error(DEV)
 
 
 def _paged(batch: int, context: int, new: int, page: int):
@@ -288,6 +300,7 @@ def main(argv=None) -> int:
     p.add_argument("--tokens", type=ints, default=[8, 2048])
     for k, v in (("width", 2048), ("ff", 2048), ("experts", 16), ("top", 6), ("groups", 1), ("keep", 1)):
         p.add_argument("--" + k, type=int, default=v)
+    p.add_argument("--mma", action="store_true", help="long row lists on the mma.sync kernel instead of tcgen05")
     p = sub.add_parser("latent-attn")
     p.add_argument("--plain", type=int, default=0)
     p.add_argument("--copies", type=int, default=4)

@@ -23,6 +23,9 @@ ops.register_signatures("mix", {
     "rllm_grouped_gemm_ragged": [c_int, c_int, _P, _LL, _P, _LL, _P, _LL, c_int, c_int, _P, _P, c_int, c_int, _P, _P, _P,
                                  _P],
     "rllm_grouped_gemm_tile_rows": [c_int, _LL, c_int, c_int],
+    "rllm_grouped_gemm_tc_supported": [_LL, c_int, c_int],
+    "rllm_grouped_gemm_tc": [c_int, _P, _LL, _LL, _P, c_int, c_int, c_int, _P, _LL, _P, _P, c_int, _P, _P, _P, _P],
+    "rllm_gather_rows_bf16": [_P, _LL, _P, _P, c_int, c_int, _P],
     "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
     "rllm_moe_plan": [_P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "rllm_rmsnorm_add": [_P, c_int, _P, _P, c_int, c_int, c_float, _P],
@@ -173,6 +176,45 @@ def grouped_gemm_ragged(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: 
         plan.rows_tok.data_ptr() if gather else None,
         plan.rows_dest.data_ptr() if scatter else None, plan.rows_scale.data_ptr() if scale else None, _stream()),
         "grouped_gemm_ragged")
+    return out
+
+
+def tc_supported(lda: int, N: int, K: int) -> bool:
+    """Does the tcgen05 grouped product take a ragged product with these sizes (bfloat16, tiles of 128 rows)?"""
+    return bool(_fn("mix", "rllm_grouped_gemm_tc_supported")(int(lda), int(N), int(K)))
+
+
+def gather_rows_bf16(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[idx[r]] for bfloat16 rows (the sorted rows a grouped product reads as one matrix)."""
+    _rows(x, "x", x.shape[1])
+    _i32(idx, "idx")
+    if x.dtype != torch.bfloat16:
+        raise KernelError("gather_rows_bf16 takes bfloat16 rows")
+    out = torch.empty((idx.numel(), x.shape[1]), dtype=torch.bfloat16, device=x.device)
+    _check(_fn("mix", "rllm_gather_rows_bf16")(x.data_ptr(), x.stride(0), idx.data_ptr(), out.data_ptr(), idx.numel(),
+                                               x.shape[1], _stream()), "gather_rows_bf16")
+    return out
+
+
+def grouped_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: torch.Tensor, epilogue: int,
+                    scatter: bool = False, scale: bool = False, err: torch.Tensor | None = None) -> torch.Tensor:
+    """The ragged product on tcgen05 (csrc/grouped_gemm_tc.cu): a [plan rows, K] bfloat16 in sorted order (no
+    gather: see gather_rows_bf16), w [E, N, K]; epilogue GEPI_RELU2 (bfloat16 out, sorted order) or
+    GEPI_STORE_F32 (float out, `scatter` to the rows' places, `scale` by their weights). The plan must have
+    tiles of 128 rows. `err`: one int32 on the device that records a bounded wait that ran out."""
+    E, N, K = w.shape
+    _rows(a, "a", K)
+    _rows(out, "out", N)
+    _cuda(w, "w")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or plan.tile_rows != 128 \
+            or a.shape[0] < plan.n_rows or epilogue not in (GEPI_RELU2, GEPI_STORE_F32):
+        raise KernelError("tcgen05 grouped product: bfloat16 operands, a plan with tiles of 128 rows, relu^2 or float store")
+    if out.dtype != (torch.float32 if epilogue == GEPI_STORE_F32 else torch.bfloat16) or out.shape[0] < plan.n_rows:
+        raise KernelError(f"tcgen05 grouped product: out has dtype {out.dtype} and {out.shape[0]} rows")
+    _check(_fn("mix", "rllm_grouped_gemm_tc")(
+        epilogue, a.data_ptr(), a.stride(0), plan.n_rows, w.data_ptr(), E, N, K, out.data_ptr(), out.stride(0),
+        plan.tiles.data_ptr(), plan.n_tiles.data_ptr(), plan.max_tiles, plan.rows_dest.data_ptr() if scatter else None,
+        plan.rows_scale.data_ptr() if scale else None, _ptr(err), _stream()), "grouped_gemm_tc")
     return out
 
 

@@ -133,7 +133,8 @@ def test_router_kernel_against_plain(E, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("T,G,K,N,W,F", [(70, 3, 20, 37, 24, 40), (300, 5, 72, 200, 136, 264), (9, 2, 128, 128, 64, 32)])
+@pytest.mark.parametrize("T,G,K,N,W,F", [(70, 3, 20, 37, 24, 40), (300, 5, 72, 200, 136, 264), (9, 2, 128, 128, 64, 32),
+                                         (900, 2, 64, 64, 256, 200)])
 def test_grouped_products(dtype, T, G, K, N, W, F):
     """Depths that are multiples of 8 run on the tensor cores in bfloat16 (tiles of 128 rows, partial tiles on
     every edge), the others and float32 on the CUDA cores; 150 or more rows over 5 experts, and 9 rows (a
@@ -170,6 +171,19 @@ def check_ragged(mix, dt, dtype, T, E, top, W, F, x, up, down, gi, gw, per_tile)
             h = (torch.relu(up[e].double() @ x[t].double()) ** 2).to(dt).double()
             want[t, s] = float(gw[t, s]) * (down[e].double() @ h)
     assert rel(parts.view(T, top, W), want) < (1e-6 if dtype == "float32" else 1e-2)
+    if per_tile == 128 and mix.tc_supported(W, F, W) and mix.tc_supported(F, W, F):
+        # the same two products on tcgen05: the sorted rows as a matrix of their own, tiles that end inside an
+        # expert's segment, inside the box and beyond the list, weight rows beyond an expert's
+        from rllm_b200.kernels import sm100
+        err = sm100.init(DEV).err
+        rows = mix.gather_rows_bf16(x.to(DEV), plan.rows_tok)
+        assert torch.equal(rows.cpu(), x[plan.rows_tok.cpu().long()])
+        act2 = torch.full((T * top, F), float("nan"), dtype=dt, device=DEV)
+        mix.grouped_gemm_tc(rows, up.to(DEV), plan, act2, mix.GEPI_RELU2, err=err)
+        parts2 = torch.full((T * top, W), float("nan"), dtype=torch.float32, device=DEV)
+        mix.grouped_gemm_tc(act2, down.to(DEV), plan, parts2, mix.GEPI_STORE_F32, scatter=True, scale=True, err=err)
+        sm100.check_error(DEV)
+        assert rel(act2, act) < 1e-2 and rel(parts2.view(T, top, W), want) < 1e-2
 
 
 # ------------------------------------------------------------------ mixers alone, over steps
