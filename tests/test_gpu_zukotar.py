@@ -273,7 +273,7 @@ def test_latent_attention_over_steps(dtype, m, page):
     assert rel(again, want_b) < tol
 
 
-@pytest.mark.parametrize("rank", [64, 128])
+@pytest.mark.parametrize("rank", [64, 128, 256, 512])
 @pytest.mark.parametrize("window", [None, 300])
 def test_latent_decoding_deals_the_keys_out_to_several_ctas(window, rank):
     """Single tokens of two sequences against 600 and 260 cached keys in bfloat16: the row tiles' keys are
@@ -292,7 +292,8 @@ def test_latent_decoding_deals_the_keys_out_to_several_ctas(window, rank):
     da, db = ha.to(DT[dtype]).to(DEV), hb.to(DT[dtype]).to(DEV)
     hs = Harness(dtype, [part.cache_spec()], page_size=16, pages=64)
     y = hs.run([("a", 600), ("b", 260)], lambda ctx, cache: part.forward(torch.cat([da[:600], db[:260]]), ctx, cache))
-    assert rel(y[:600], want["a"][:600]) < 2.5e-2 and rel(y[600:], want["b"][:260]) < 2.5e-2
+    tol = 2.5e-2 if rank <= 128 else 4e-2       # bfloat16 latents: the rounding of a sum over `rank` numbers grows with it
+    assert rel(y[:600], want["a"][:600]) < tol and rel(y[600:], want["b"][:260]) < tol
     seen = []
     for i in range(6):
         def step(ctx, cache):
@@ -303,12 +304,13 @@ def test_latent_decoding_deals_the_keys_out_to_several_ctas(window, rank):
             seen.append(max(1, min(16, ctx.backend.sm_count // tiles, keys // 128)))
             return part.forward(torch.cat([da[600 + i: 601 + i], db[260 + i: 261 + i]]), ctx, cache)
         y = hs.run([("a", 1), ("b", 1)], step)
-        assert rel(y[:1], want["a"][600 + i: 601 + i]) < 2.5e-2 and rel(y[1:], want["b"][260 + i: 261 + i]) < 2.5e-2
+        assert rel(y[:1], want["a"][600 + i: 601 + i]) < tol and rel(y[1:], want["b"][260 + i: 261 + i]) < tol
     assert min(seen) >= 2            # the steps above did run with their keys split
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("H,d,v,tau,r", [(3, 20, 24, 6.0, 8), (1, 64, 72, 2.5, 16), (2, 36, 44, 16.0, 8), (2, 130, 33, 40.0, 4)])
+@pytest.mark.parametrize("H,d,v,tau,r", [(3, 20, 24, 6.0, 8), (1, 64, 72, 2.5, 16), (2, 36, 44, 16.0, 8), (2, 130, 33, 40.0, 4),
+                                         (2, 128, 40, 20.0, 8), (1, 100, 33, 12.0, 4), (1, 256, 32, 30.0, 8)])
 def test_gla_over_steps_and_slots(dtype, H, d, v, tau, r):
     """Decays near one (large tau, positive bias) keep the first tokens in the state for the whole
     sequence; a request that takes over a slot must not see what its predecessor left there."""

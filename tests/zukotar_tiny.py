@@ -59,9 +59,17 @@ ZD = {  # recurrent layers only (no pages at all), all of them looped, one witho
     ],
     "loop": {"start": 0, "stop": 2, "times": 2},
 }
+ZE = {  # nothing a multiple of 8: width 100, vocabulary 77, cache rows of 26 numbers, 7 experts
+    "architecture": "Zukotar", "vocab": 77, "width": 100, "embedding": {"scale": 10.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "latent_attention", "mixer": latent(3, 10, 6, 14, 20, 0.25, 10000.0, 6, 19), "mlp": moe(12, 7, 2)},
+        {"type": "gla", "mixer": {"heads": 3, "dim": 14, "vdim": 10, "tau": 4.0, "decay_rank": 6}, "mlp": moe(20, 7, 3)},
+    ],
+    "loop": {"start": 0, "stop": 1, "times": 2},
+}
 # name -> (config, seed, weight std, norm std, page size)
 TINY = {"ZA": (ZA, 11, 0.09, 0.2, 4), "ZB": (ZB, 12, 0.12, 0.1, 8), "ZC": (ZC, 13, 0.1, 0.3, 16),
-        "ZD": (ZD, 14, 0.15, 0.2, 16)}
+        "ZD": (ZD, 14, 0.15, 0.2, 16), "ZE": (ZE, 15, 0.1, 0.2, 8)}
 
 
 def make_model_dir(root, name, dtype=torch.bfloat16):
