@@ -9,7 +9,7 @@
 //
 // gla_scan (mode WHOLE): one CTA per (sequence, head, 32 value columns); the four warps split the key
 //   channels, a lane owns a value column and keeps its share of S in registers while it walks the sequence's
-//   tokens, eight at a time through shared memory. The four warps' partial sums of o are added in warp order.
+//   tokens, sixteen at a time through shared memory. The four warps' partial sums of o are added in warp order.
 //   A position's result is the same bits whether its tokens came one by one or in portions.
 // Long portions (the caller decides by the longest portion of the step) are cut into chunks of `chunk` tokens
 //   that run side by side, which the recurrence allows because it is linear in S: with A_c the product of
@@ -24,7 +24,7 @@ using namespace rllm;
 
 namespace {
 
-constexpr int CH = 8;            // tokens staged at a time
+constexpr int CH = 16;           // tokens staged at a time, at most (8 for heads of more than 128 key channels)
 constexpr int MAX_DIM = 256;     // key channels per head
 enum : int { WHOLE = 0, LOCAL = 1, FINAL = 2 };
 
@@ -56,10 +56,10 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
                 const float* __restrict__ alpha, float qscale, int H, int dim, int vdim,
                 const int* __restrict__ cu_q, int num_seqs, const int* __restrict__ state_slots,
                 float* __restrict__ state, float* __restrict__ out, int chunk, float* __restrict__ chunk_state,
-                float* __restrict__ chunk_decay) {
+                float* __restrict__ chunk_decay, int ch) {
   pdl_launch();
   pdl_wait();
-  __shared__ __align__(16) float qs[CH][MAX_DIM], ks[CH][MAX_DIM], as[CH][MAX_DIM];
+  extern __shared__ __align__(16) float staged[];              // queries, keys, decays: [ch][dimp] each
   __shared__ float vs[CH][32];
   __shared__ float part[CH][4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -69,6 +69,10 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
   int row0 = cu_q[seq], row1 = cu_q[seq + 1];
   if (MODE != WHOLE) { row0 += c * chunk; row1 = min(row1, row0 + chunk); }
   const int slot = (MODE == WHOLE && state_slots) ? state_slots[seq] : -1;
+  const int dimp = (dim + 3) & ~3;               // a staged row, padded to 16 bytes
+  float* qs = staged;
+  float* ks = qs + ch * dimp;
+  float* as = ks + ch * dimp;
   const int kp = (dim + 3) / 4;                  // key channels of a warp
   const int kbase = warp * kp;
   const bool vok = v < vdim;
@@ -84,14 +88,41 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
     S[i] = ((MODE == WHOLE ? slot >= 0 : MODE == FINAL) && mine) ? sp[(long long)k * vdim] : 0.f;
     if (MODE == LOCAL) A[i] = 1.f;
   }
-  for (int c0 = row0; c0 < row1; c0 += CH) {
-    const int n = min(CH, row1 - c0);
-    for (int x = threadIdx.x; x < n * dim; x += 128) {
-      const int cc = x / dim, k = x % dim;
-      const TI* r = proj + (long long)(c0 + cc) * ld;
-      if (MODE != LOCAL) qs[cc][k] = to_f32(r[q_off + h * dim + k]) * qscale;
-      ks[cc][k] = to_f32(r[k_off + h * dim + k]);
-      as[cc][k] = alpha[(long long)(c0 + cc) * H * dim + h * dim + k];
+  // bfloat16 rows whose pieces of 8 channels are 16-byte aligned are staged 8 channels a load
+  const bool wide = sizeof(TI) == 2 && dim % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 &&
+                    !((uintptr_t)proj & 15) && !((uintptr_t)alpha & 15);
+  for (int c0 = row0; c0 < row1; c0 += ch) {
+    const int n = min(ch, row1 - c0);
+    if (wide) {
+      const int per = dim >> 3;
+      for (int x = threadIdx.x; x < n * per; x += 128) {
+        const int cc = x / per, k = (x % per) * 8;
+        const TI* r = proj + (long long)(c0 + cc) * ld;
+        const float4* ap = reinterpret_cast<const float4*>(alpha + (long long)(c0 + cc) * H * dim + h * dim + k);
+        const uint4 kq = *reinterpret_cast<const uint4*>(r + k_off + h * dim + k);
+        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kq);
+        float* kd = ks + cc * dimp + k;
+        float* ad = as + cc * dimp + k;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(kh[e]); kd[2 * e] = f.x; kd[2 * e + 1] = f.y; }
+        *reinterpret_cast<float4*>(ad) = ap[0];
+        *reinterpret_cast<float4*>(ad + 4) = ap[1];
+        if (MODE != LOCAL) {
+          const uint4 qq = *reinterpret_cast<const uint4*>(r + q_off + h * dim + k);
+          const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qq);
+          float* qd = qs + cc * dimp + k;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(qh[e]); qd[2 * e] = f.x * qscale; qd[2 * e + 1] = f.y * qscale; }
+        }
+      }
+    } else {
+      for (int x = threadIdx.x; x < n * dim; x += 128) {
+        const int cc = x / dim, k = x % dim;
+        const TI* r = proj + (long long)(c0 + cc) * ld;
+        if (MODE != LOCAL) qs[cc * dimp + k] = to_f32(r[q_off + h * dim + k]) * qscale;
+        ks[cc * dimp + k] = to_f32(r[k_off + h * dim + k]);
+        as[cc * dimp + k] = alpha[(long long)(c0 + cc) * H * dim + h * dim + k];
+      }
     }
     for (int x = threadIdx.x; x < n * 32; x += 128) {
       const int cc = x >> 5, j = x & 31;
@@ -103,9 +134,9 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
       // a warp's key channels are a multiple of 4: decays, keys and queries come four at a time
       for (int cc = 0; cc < n; ++cc) {
         const float val = vs[cc][lane];
-        const float4* a4 = reinterpret_cast<const float4*>(&as[cc][kbase]);
-        const float4* k4 = reinterpret_cast<const float4*>(&ks[cc][kbase]);
-        const float4* q4 = reinterpret_cast<const float4*>(&qs[cc][kbase]);
+        const float4* a4 = reinterpret_cast<const float4*>(as + cc * dimp + kbase);
+        const float4* k4 = reinterpret_cast<const float4*>(ks + cc * dimp + kbase);
+        const float4* q4 = reinterpret_cast<const float4*>(qs + cc * dimp + kbase);
         float o = 0.f;
 #pragma unroll
         for (int i = 0; i < KP; i += 4) {
@@ -130,9 +161,9 @@ gla_scan_kernel(const TI* __restrict__ proj, long long ld, int q_off, int k_off,
         for (int i = 0; i < KP; ++i) {
           const int k = kbase + i;
           if (i < kp && k < dim) {
-            S[i] = fmaf(as[cc][k], S[i], ks[cc][k] * val);
-            if (MODE == LOCAL) A[i] *= as[cc][k];
-            else o = fmaf(S[i], qs[cc][k], o);
+            S[i] = fmaf(as[cc * dimp + k], S[i], ks[cc * dimp + k] * val);
+            if (MODE == LOCAL) A[i] *= as[cc * dimp + k];
+            else o = fmaf(S[i], qs[cc * dimp + k], o);
           }
         }
         if (MODE != LOCAL) part[cc][warp][lane] = o;
@@ -216,11 +247,14 @@ gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ w, floa
 template <typename TI, int MODE>
 int scan(dim3 grid, cudaStream_t s, const void* proj, long long ld, int q_off, int k_off, int v_off, const float* alpha,
          float qscale, int H, int dim, int vdim, const int* cu_q, int num_seqs, const int* state_slots, float* state,
-         float* out, int chunk, float* chunk_state, float* chunk_decay) {
+         float* out, int chunk, float* chunk_state, float* chunk_decay, int T) {
   const int kp = (dim + 3) / 4;
+  // tokens staged at a time: 16 (8 for wide heads), 2 for steps of single tokens (the room goes to more CTAs an SM)
+  const int ch = T <= 2 * num_seqs ? 2 : (dim <= 128 ? CH : CH / 2);
+  const size_t smem = (size_t)3 * ch * ((dim + 3) & ~3) * sizeof(float);                             // at most 24 KB
 #define GO(KP)                                                                                                        \
-  return launch_ex(gla_scan_kernel<TI, KP, MODE>, grid, dim3(128), 0, s, 1, (const TI*)proj, ld, q_off, k_off, v_off, \
-                   alpha, qscale, H, dim, vdim, cu_q, num_seqs, state_slots, state, out, chunk, chunk_state, chunk_decay)
+  return launch_ex(gla_scan_kernel<TI, KP, MODE>, grid, dim3(128), smem, s, 1, (const TI*)proj, ld, q_off, k_off, v_off, \
+                   alpha, qscale, H, dim, vdim, cu_q, num_seqs, state_slots, state, out, chunk, chunk_state, chunk_decay, ch)
   if (kp <= 8) GO(8);
   if (kp <= 16) GO(16);
   if (kp <= 32) GO(32);
@@ -256,9 +290,9 @@ RLLM_API int rllm_gla_scan(int dt, const void* proj, long long ld, int q_off, in
   const int vb = (vdim + 31) / 32;
 #define SCAN(MODE, GRID)                                                                                            \
   (dt == DT_F32 ? scan<float, MODE>(GRID, s, proj, ld, q_off, k_off, v_off, alpha, qscale, H, dim, vdim, cu_q, S,   \
-                                    state_slots, state, out, chunk, chunk_state, chunk_decay)                       \
+                                    state_slots, state, out, chunk, chunk_state, chunk_decay, T)                    \
                 : scan<bf16, MODE>(GRID, s, proj, ld, q_off, k_off, v_off, alpha, qscale, H, dim, vdim, cu_q, S,    \
-                                   state_slots, state, out, chunk, chunk_state, chunk_decay))
+                                   state_slots, state, out, chunk, chunk_state, chunk_decay, T))
   if (chunk <= 0) return SCAN(WHOLE, dim3(S, H, vb));
   if (!chunk_state || !chunk_decay) return ERR_BAD_SIZE;
   const int chunks = T / chunk + S;                                  // at least as many as the sequences have
