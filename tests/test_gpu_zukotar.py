@@ -233,7 +233,10 @@ def test_latent_attention_over_steps(dtype, m, page):
     W, n = 40, 97
     w = latent_weights(W, m, seed=m["heads"])
     h = rnd(n, W, seed=9)
-    for p in (0, 1, page - 1, page, 2 * page + 1, 50, 96 - (m.get("mask") or {"size": 30})["size"]):
+    size = (m.get("mask") or {"size": 30})["size"]
+    # the last query (position 96, part of the prompt or decoded alone) has one of them just outside its window and
+    # one just inside; so has query 70
+    for p in {0, 1, page - 1, page, 2 * page + 1, 50, 96 - size, 97 - size, max(0, 70 - size), max(0, 71 - size)}:
         h[p] *= 6.0
     want = P.latent_attention(h.to(DT[dtype]).double(), as_stored(w, dtype), "x.", m, 1e-6)
     win = m["mask"]["size"] if "mask" in m else None
@@ -241,7 +244,9 @@ def test_latent_attention_over_steps(dtype, m, page):
                            InterleavedRotary(m["rot_dim"], m["rot"]["base"], m["rot"]["dims"]), window=win, eps=1e-6)
     bind(part, w, dtype, "x.")
     hd = h.to(DT[dtype]).to(DEV)
-    tol = 2e-5 if dtype == "float32" else 2.5e-2
+    # bfloat16: where two scaled-up keys compete for a query, the rounding of their scores shows in the weights;
+    # a key wrongly seen or lost moves a row by its whole size
+    tol = 2e-5 if dtype == "float32" else 4e-2
     outs = {}
     for name, sched in SCHEDULES.items():
         hs = Harness(dtype, [part.cache_spec()], page_size=page, pages=2 + (n + page - 1) // page)
