@@ -3,7 +3,7 @@ group of layers with equal needs, and slots of fixed-size per-request state.
 
 How a layer's need is served is looked up by the class of its spec (`parts.base.CacheKind`,
 `register_cache_kind`); the manager knows no spec class by name. Layers of a paged kind are
-grouped by equal specs (`KVCacheSpec`: kv heads, head size, window). Each group has pages of its
+grouped by equal specs (`KVCacheSpec`: kv heads, head sizes, window, block rule). Each group has pages of its
 own, and a pool of its own size: a group that keeps every key grows with the request, a group
 with a window gives pages back as soon as the window has passed them, and the pages of a request
 that ends return at once and are handed out again. Layers of a slot kind (`StateSpec`) get one
@@ -141,6 +141,10 @@ class CacheManager:
         self._ptr = self._L.cache_new(G, counts, windows, page_size, max_requests)
         if not self._ptr:
             raise ValueError("the native cache tables could not be made")
+        for gi, gs in enumerate(group_specs):
+            chunk = cache_kind_of(gs).chunk(gs)
+            if chunk is not None and self._L.cache_set_chunk(self._ptr, gi, int(chunk)):
+                raise ValueError(f"cache group {gi}: a block rule of {chunk} positions was refused")
         self.holders = Holders()
         for gi, (gs, layers) in enumerate(zip(group_specs, group_layers)):
             pool = PagePool(pages_of[gi], _ptr=self._L.cache_pool(self._ptr, gi), _holders=self.holders, _owner=self)
@@ -195,9 +199,11 @@ class CacheManager:
 
     def first_needed_page(self, group: CacheGroup, num_tokens: int) -> int:
         """Pages below this index hold only keys that no later query can see."""
-        if group.spec.window is None:
-            return 0
-        first_key = num_tokens - group.spec.window + 1   # oldest key the next query sees
+        kind = cache_kind_of(group.spec)
+        window, chunk = kind.window(group.spec), kind.chunk(group.spec)
+        first_key = 0 if window is None else num_tokens - window + 1   # oldest key the next query sees
+        if chunk:
+            first_key = max(first_key, num_tokens // chunk * chunk)
         return max(0, first_key // self.page_size)
 
     def pages_needed(self, rc: RequestCache, new_total: int) -> list[int]:

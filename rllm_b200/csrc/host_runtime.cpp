@@ -74,12 +74,13 @@ struct Cache {
   int page_size;
   std::vector<Pool> pools;           // per group
   std::vector<int> window;           // per group, < 0: every key is kept
+  std::vector<int> chunk;            // per group, > 0: a query sees only its own block of this many positions
   Pool slots;
   std::vector<Holding> held;         // by state slot
   long long serials = 0;
   Cache(int G, const int* num_pages, const int* windows, int ps, int max_requests)
       : page_size(ps), slots(max_requests), held((size_t)max_requests) {
-    for (int g = 0; g < G; ++g) { pools.emplace_back(num_pages[g]); window.push_back(windows[g]); }
+    for (int g = 0; g < G; ++g) { pools.emplace_back(num_pages[g]); window.push_back(windows[g]); chunk.push_back(0); }
   }
   int pages_for(int tokens) const { return (tokens + page_size - 1) / page_size; }
 };
@@ -120,6 +121,14 @@ RLLM_API void* rllm_cache_new(int groups, const int* num_pages, const int* windo
   return new Cache(groups, num_pages, windows, page_size, max_requests);
 }
 RLLM_API void rllm_cache_delete(void* c) { delete static_cast<Cache*>(c); }
+// Group `group` serves layers whose queries see only their own block of `chunk` positions (blocks counted from
+// position 0): the pages before the block of the next position go back to the pool in commit. 0: no such rule.
+RLLM_API int rllm_cache_set_chunk(void* cv, int group, int chunk) {
+  Cache* c = static_cast<Cache*>(cv);
+  if (group < 0 || group >= (int)c->pools.size() || chunk < 0) return -1;
+  c->chunk[(size_t)group] = chunk;
+  return 0;
+}
 RLLM_API void* rllm_cache_pool(void* c, int group) { return &static_cast<Cache*>(c)->pools[(size_t)group]; }
 RLLM_API void* rllm_cache_slots(void* c) { return &static_cast<Cache*>(c)->slots; }
 
@@ -178,8 +187,12 @@ RLLM_API int rllm_cache_commit(void* cv, int handle, int new_total) {
     if (total > (int)h->pages[g].size()) return -2;
   h->num_tokens = new_total;
   for (size_t g = 0; g < c->pools.size(); ++g) {
-    if (c->window[g] < 0) continue;
-    const int first_key = new_total - c->window[g] + 1;           // oldest key the next query sees
+    if (c->window[g] < 0 && c->chunk[g] <= 0) continue;
+    int first_key = c->window[g] < 0 ? 0 : new_total - c->window[g] + 1;   // oldest key the next query sees
+    if (c->chunk[g] > 0) {
+      const int block_start = new_total / c->chunk[g] * c->chunk[g];
+      if (block_start > first_key) first_key = block_start;
+    }
     int last = first_key > 0 ? first_key / c->page_size : 0;
     if (last > (int)h->pages[g].size()) last = (int)h->pages[g].size();
     for (int i = 0; i < last; ++i) {

@@ -1,6 +1,7 @@
 // Routing of a mixture of experts, and the norm that follows a sublayer.
 //
-// moe_topk: per token, from float router logits [T, E]: scores = softmax over all experts; experts form
+// moe_topk: per token, from float router logits [T, E]: scores = softmax over all experts (score_fn 0) or
+//   sigmoid of each logit by itself (score_fn 1); experts form
 //   `groups` equal groups of neighbours, a group's score is its largest, only experts of the best `keep`
 //   groups can be chosen (groups <= 1: no such limit); the `top` largest scores are chosen; their weights
 //   are the scores themselves, or the scores divided by their sum (`renorm`). All in float. Of equal
@@ -19,8 +20,8 @@ namespace {
 constexpr int MAX_E = 1024;      // experts a warp can rank (32 per lane)
 
 __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int groups,
-                                                       int keep, int top, int renorm, int* __restrict__ idx,
-                                                       float* __restrict__ wt) {
+                                                       int keep, int top, int renorm, int score_fn,
+                                                       int* __restrict__ idx, float* __restrict__ wt) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];            // per warp: E scores, then E flags (1 allowed)
@@ -30,14 +31,18 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   float* s = sm + (size_t)warp * 2 * E;
   float* ok = s + E;
   const float* z = logits + (size_t)t * E;
-  float m = -INFINITY;
-  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-  m = warp_max(m);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); s[e] = v; sum += v; }
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int e = lane; e < E; e += 32) { s[e] *= inv; ok[e] = 1.f; }
+  if (score_fn == 1) {
+    for (int e = lane; e < E; e += 32) { s[e] = 1.f / (1.f + expf(-z[e])); ok[e] = 1.f; }
+  } else {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); s[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E; e += 32) { s[e] *= inv; ok[e] = 1.f; }
+  }
   __syncwarp();
   if (groups > 1 && keep < groups) {
     const int per = E / groups;
@@ -144,14 +149,14 @@ __global__ void add_row_kernel(float* __restrict__ h, const float* __restrict__ 
 
 }  // namespace
 
-RLLM_API int rllm_moe_topk(const float* logits, int T, int E, int groups, int keep, int top, int renorm, int* idx,
-                           float* wt, void* stream) {
+RLLM_API int rllm_moe_topk(const float* logits, int T, int E, int groups, int keep, int top, int renorm, int score_fn,
+                           int* idx, float* wt, void* stream) {
   if (T <= 0) return 0;
-  if (E <= 0 || E > MAX_E || top <= 0 || top > 32 || top > E) return ERR_BAD_SIZE;
+  if (E <= 0 || E > MAX_E || top <= 0 || top > 32 || top > E || score_fn < 0 || score_fn > 1) return ERR_BAD_SIZE;
   if (groups > 1 && (E % groups || keep <= 0 || keep > groups || top > (E / groups) * keep)) return ERR_BAD_SIZE;
   const size_t smem = (size_t)4 * 2 * E * sizeof(float);
   return launch_ex(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), smem, (cudaStream_t)stream, 1, logits, T, E, groups,
-                   keep, top, renorm, idx, wt);
+                   keep, top, renorm, score_fn, idx, wt);
 }
 
 // tiles: room for n / tile_rows + E entries of 3 ints.

@@ -1,0 +1,130 @@
+// Row-wise work on the float residual stream for layers that norm after the sum, and the small
+// activations of their feed-forwards.
+//
+// postnorm:  s = alpha * h[t] + sum over p of y[t, p, :] (+ sigmoid(zg[t]) * y2[t]);  h[t] = w * s / sqrt(mean(s^2) + eps),
+//            float throughout, the parts added in order. Also writes h[t] in the run's storage type (`copy`),
+//            which is what the next sublayer's products read.
+// cast_rows: the stream in the run's storage type (the first layer's input).
+// gated_act: out[r, i] = act(scale_r * gu[r, i]) * (scale_r * gu[r, F + i]) for gu [R, 2F] (float or storage type),
+//            act = silu. relu2: x <- max(x, 0)^2 in place.
+#include "common.cuh"
+using namespace rllm;
+
+namespace {
+
+template <typename TO>
+__global__ void postnorm_kernel(float* __restrict__ h, const float* __restrict__ y, int parts, const float* __restrict__ y2,
+                                const float* __restrict__ zg, int zg_ld, float alpha, const float* __restrict__ w, int H,
+                                float eps, TO* __restrict__ copy) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const size_t t = blockIdx.x;
+  float* hr = h + t * H;
+  const float* yr = y ? y + t * parts * H : nullptr;
+  const float* y2r = y2 ? y2 + t * H : nullptr;
+  const float g2 = (y2 && zg) ? 1.f / (1.f + expf(-zg[t * zg_ld])) : 1.f;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = alpha * hr[i];
+    if (yr)
+      for (int p = 0; p < parts; ++p) v += yr[(size_t)p * H + i];
+    if (y2r) v = fmaf(g2, y2r[i], v);
+    row[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = row[i] * r * w[i];
+    hr[i] = v;
+    if (copy) copy[t * H + i] = from_f32<TO>(v);
+  }
+}
+
+__global__ void cast_rows_kernel(const float* __restrict__ x, bf16* __restrict__ out, long long n) {
+  pdl_launch();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(x[i]);
+}
+
+template <typename TI, typename TO>
+__global__ void gated_act_kernel(const TI* __restrict__ gu, long long ld, TO* __restrict__ out, int F, long long n,
+                                 const float* __restrict__ row_scale) {
+  pdl_launch();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / F;
+    const int c = (int)(i % F);
+    const float f = row_scale ? row_scale[r] : 1.f;
+    const float g = f * to_f32(gu[r * ld + c]), u = f * to_f32(gu[r * ld + F + c]);
+    out[i] = from_f32<TO>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ x, long long n) {
+  pdl_launch();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_f32(x[i]), 0.f);
+    x[i] = from_f32<T>(v * v);
+  }
+}
+
+inline int blocks_for(long long n) { return (int)((n + 255) / 256 < 2368 ? (n + 255) / 256 : 2368); }
+
+}  // namespace
+
+// h [T, H] float in place; y [T, parts, H] float or null; y2 [T, H] float or null with zg (logits, one per row at
+// stride zg_ld) or null; copy [T, H] of type copy_dt or null.
+RLLM_API int rllm_postnorm(float* h, const float* y, int parts, const float* y2, const float* zg, int zg_ld, float alpha,
+                           const float* w, int T, int H, float eps, void* copy, int copy_dt, void* stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || parts < 0 || (size_t)H * sizeof(float) > 200 * 1024) return ERR_BAD_SIZE;
+  const int smem = H * (int)sizeof(float);
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (copy && copy_dt == DT_BF16) {
+    static bool done[64] = {};
+    if (smem > 48 * 1024) { const int rc = allow_dynamic_smem(postnorm_kernel<bf16>, smem, done); if (rc) return rc; }
+    return launch_ex(postnorm_kernel<bf16>, dim3(T), dim3(threads), (size_t)smem, s, 1, h, y, parts, y2, zg, zg_ld, alpha, w,
+                     H, eps, (bf16*)copy);
+  }
+  if (copy && copy_dt != DT_F32) return ERR_BAD_DTYPE;
+  static bool done[64] = {};
+  if (smem > 48 * 1024) { const int rc = allow_dynamic_smem(postnorm_kernel<float>, smem, done); if (rc) return rc; }
+  return launch_ex(postnorm_kernel<float>, dim3(T), dim3(threads), (size_t)smem, s, 1, h, y, parts, y2, zg, zg_ld, alpha, w,
+                   H, eps, (float*)copy);
+}
+
+RLLM_API int rllm_cast_rows(const float* x, void* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  return launch_ex(cast_rows_kernel, dim3(blocks_for(n)), dim3(256), 0, (cudaStream_t)stream, 1, x, (bf16*)out, n);
+}
+
+// gu [R, >= 2F] of type in_dt with row stride ld -> out [R, F] of type out_dt; row_scale float [R] or null.
+RLLM_API int rllm_gated_act(const void* gu, int in_dt, long long ld, void* out, int out_dt, int R, int F,
+                            const float* row_scale, void* stream) {
+  if (R <= 0 || F <= 0) return 0;
+  const long long n = (long long)R * F;
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 g(blocks_for(n)), b(256);
+  if (in_dt == DT_F32 && out_dt == DT_F32)
+    return launch_ex(gated_act_kernel<float, float>, g, b, 0, s, 1, (const float*)gu, ld, (float*)out, F, n, row_scale);
+  if (in_dt == DT_F32 && out_dt == DT_BF16)
+    return launch_ex(gated_act_kernel<float, bf16>, g, b, 0, s, 1, (const float*)gu, ld, (bf16*)out, F, n, row_scale);
+  if (in_dt == DT_BF16 && out_dt == DT_BF16)
+    return launch_ex(gated_act_kernel<bf16, bf16>, g, b, 0, s, 1, (const bf16*)gu, ld, (bf16*)out, F, n, row_scale);
+  return ERR_BAD_DTYPE;
+}
+
+RLLM_API int rllm_relu2(void* x, int dt, long long n, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dt == DT_F32) return launch_ex(relu2_kernel<float>, dim3(blocks_for(n)), dim3(256), 0, s, 1, (float*)x, n);
+  if (dt == DT_BF16) return launch_ex(relu2_kernel<bf16>, dim3(blocks_for(n)), dim3(256), 0, s, 1, (bf16*)x, n);
+  return ERR_BAD_DTYPE;
+}

@@ -203,9 +203,9 @@ class Backend:
         down = self._mix.tile_rows(x.dtype, w_down.shape[2], w_down.shape[2], n_rows)
         return up if up == down else 64         # one of them stays on the CUDA cores: both take its tiles
 
-    def route(self, logits, top, groups=1, keep=1, renorm=False, tile_rows=64):
+    def route(self, logits, top, groups=1, keep=1, renorm=False, tile_rows=64, score="softmax"):
         """Router logits -> the plan of the experts' grouped products (all on the device)."""
-        idx, wt = self._mix.moe_topk(logits, top, groups, keep, renorm)
+        idx, wt = self._mix.moe_topk(logits, top, groups, keep, renorm, score)
         return idx, wt, self._mix.moe_plan(idx, wt, logits.shape[1], tile_rows)
 
     def _tc_experts(self, a, w, plan):
@@ -224,16 +224,86 @@ class Backend:
                                              err=self._sm100.init(self.device).err)
         return self._mix.grouped_gemm_ragged(x, w_up, plan, out, self._mix.GEPI_RELU2, gather=True)
 
-    def experts_down(self, a, w_down, plan, T, top):
-        """weight of row * (a[row] W_down[expert of row]^T), stored at the row's (token, slot): float
-        [T, top, width], every place written exactly once."""
-        out = torch.empty((T * top, w_down.shape[1]), dtype=torch.float32, device=a.device)
-        if self._tc_experts(a, w_down, plan):
-            self._mix.grouped_gemm_tc(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=True,
+    def experts_gated_up(self, x, w_gate_up, plan):
+        """silu(f g) * (f u) for every sorted row of the plan, with [g | u] = x[token of row] W[expert of row]^T
+        (W [E, 2F, K]: an expert's gate rows, then its up rows) and f the row's weight: the weight on the
+        expert's input, applied in float to the two linear projections."""
+        F2 = w_gate_up.shape[1]
+        if self._tc_experts(x, w_gate_up, plan):
+            rows = self._mix.gather_rows_bf16(x, plan.rows_tok)
+            gu = torch.empty((plan.n_rows, F2), dtype=torch.float32, device=x.device)
+            self._mix.grouped_gemm_tc(rows, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32,
                                       err=self._sm100.init(self.device).err)
         else:
-            self._mix.grouped_gemm_ragged(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=True)
+            gu = torch.empty((plan.n_rows, F2), dtype=torch.float32, device=x.device)
+            self._mix.grouped_gemm_ragged(x, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32, gather=True)
+        return self._sink.gated_act(gu, x.dtype, plan.rows_scale)
+
+    def experts_down(self, a, w_down, plan, T, top, scale=True):
+        """(weight of row, if `scale`) * (a[row] W_down[expert of row]^T), stored at the row's (token, slot):
+        float [T, top, width], every place written exactly once."""
+        out = torch.empty((T * top, w_down.shape[1]), dtype=torch.float32, device=a.device)
+        if self._tc_experts(a, w_down, plan):
+            self._mix.grouped_gemm_tc(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=scale,
+                                      err=self._sm100.init(self.device).err)
+        else:
+            self._mix.grouped_gemm_ragged(a, w_down, plan, out, self._mix.GEPI_STORE_F32, scatter=True, scale=scale)
         return out.view(T, top, w_down.shape[1])
+
+    # ---- layers that norm after the sum; attention with query/key norm, sink, gate and block mask (library "sink")
+    @property
+    def _sink(self):
+        from . import sink
+        return sink
+
+    def stream_copy(self, h):
+        """The float stream in the run's storage type: what a sublayer that reads the stream itself multiplies."""
+        return h if self.dtype == torch.float32 else self._sink.cast_rows(h)
+
+    def postnorm(self, h, y, alpha, w, eps):
+        """h <- w * s / rms(s), s = alpha h + y, in float and in place; y a float tensor [T, H] / [T, parts, H] or
+        `Summands`. Returns the new stream in the run's storage type (h itself in the 32-bit run)."""
+        parts, extra, gate = (y.parts, y.extra, y.extra_gate) if hasattr(y, "parts") else (y, None, None)
+        copy = None if self.dtype == torch.float32 else torch.empty(h.shape, dtype=self.dtype, device=h.device)
+        self._sink.postnorm(h, parts, alpha, w, eps, extra, gate, copy)
+        return h if copy is None else copy
+
+    def linear_act(self, x, w, act):
+        """act(x W^T) in the run dtype; act "relu2" = max(., 0)^2."""
+        if act != "relu2":
+            raise ops.KernelError(f"activation {act!r} has no kernel")
+        return self._sink.relu2_(self.linear(x, w))
+
+    def qk_norm_rope_store(self, proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table, cache):
+        writes = cache.writes
+        self._sink.qk_norm_rope_store(proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table,
+                                      cache.slots if writes else None, cache.k if writes else None,
+                                      cache.v if writes else None)
+
+    def sink_attention(self, q, cache, ctx, nh, scale, window, chunk, sinks, gate):
+        """Attention with a window and/or block mask, a sink and an output gate over pages whose keys and values
+        may differ in size: bfloat16 on the tensor cores where the kernel takes the sizes, else (and in the
+        32-bit run) in float on the CUDA cores."""
+        sk = self._sink
+        kd, vd = cache.k.shape[3], cache.v.shape[3]
+        if self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1" and \
+                sk.mma_supported(q.dtype, kd, vd, cache.page_size):
+            # keys a query of this step can see at most, known without a device read (graph captures included)
+            keys = ctx.max_kv_len
+            if window:
+                keys = min(keys, window + ctx.max_q_len)
+            if chunk:
+                keys = min(keys, chunk)
+            G = nh // cache.k.shape[1]
+            tiles = 0
+            for ql in (ctx.q_lens_host if not ctx.graph_safe else [1] * ctx.num_seqs):
+                tiles += (ql * G + 63) // 64
+            tiles *= cache.k.shape[1]
+            splits = max(1, min(16, self.sm_count // max(tiles, 1), keys // 128))
+            return sk.sink_attention_mma(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, ctx.cu_q,
+                                         ctx.num_seqs, ctx.max_q_len, nh, scale, window, chunk, sinks, gate, splits, keys)
+        return sk.sink_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, nh, scale,
+                                      window, chunk, sinks, gate)
 
     def latent_prepare(self, *a, **k):
         return self._mix.latent_prepare(*a, **k)

@@ -25,13 +25,17 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 
 # library name -> sources. "simt" holds the generic kernels of both precisions;
 # "sm100" the tcgen05/TMA kernels that only the bfloat16 path calls; "host" the native
-# bookkeeping of the cache manager (plain C++, no device code); "mix" the mixers and feed-forwards
-# beyond grouped-query attention and SwiGLU (latent attention, gated linear attention, routed experts),
-# both precisions, built only when a model uses them.
+# bookkeeping of the cache manager (plain C++, no device code); "mix" the mixers
+# beyond grouped-query attention (latent attention, gated linear attention), "experts" the routed feed-forwards
+# (grouped products, routing, the norm after a sublayer), "sink" grouped-query attention with query/key norm,
+# sink, output gate and block mask plus the row-wise work of layers that norm after the sum; all in both
+# precisions, each built only when a model uses it.
 LIBRARIES: dict[str, list[str]] = {
     "simt": ["simt_basic.cu", "simt_gemm.cu", "simt_attention.cu", "sampling.cu"],
     "sm100": ["tc_gemm.cu", "stream_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu", "wait_probe.cu"],
-    "mix": ["grouped_gemm.cu", "grouped_gemm_tc.cu", "moe_route.cu", "latent_attention.cu", "gla.cu"],
+    "mix": ["latent_attention.cu", "gla.cu"],
+    "experts": ["grouped_gemm.cu", "grouped_gemm_tc.cu", "moe_route.cu"],
+    "sink": ["sink_attention.cu", "stream_ops.cu"],
     "host": ["host_runtime.cpp"],          # no CUDA: the cache manager's bookkeeping and metadata writer
 }
 

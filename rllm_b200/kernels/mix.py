@@ -1,7 +1,7 @@
-"""Python face of the library "mix": sequence mixers other than grouped-query attention (attention
-over a cache of compressed latents, gated linear attention as a recurrence over per-request state),
-routed feed-forwards (top-k routing with limited groups, the plan of a grouped product, the grouped
-product itself) and the norm that follows a sublayer. Like `ops`, every function checks shapes,
+"""Python face of the libraries "mix" (sequence mixers other than grouped-query attention: attention
+over a cache of compressed latents, gated linear attention as a recurrence over per-request state)
+and "experts" (routed feed-forwards: top-k routing with limited groups, the plan of a grouped product,
+the grouped product itself, and the norm that follows a sublayer). Like `ops`, every function checks shapes,
 dtypes and devices and then calls an `extern "C"` launcher on torch's current stream; there is no
 CPU or library path behind them.
 """
@@ -17,7 +17,7 @@ from .ops import KernelError, _check, _cuda, _dt, _fn, _ptr, _stream
 _P, _LL = ops._P, c_longlong
 GEPI_STORE, GEPI_STORE_F32, GEPI_RELU2 = 0, 1, 2
 
-ops.register_signatures("mix", {
+ops.register_signatures("experts", {
     "rllm_grouped_gemm_uniform": [c_int, c_int, _P, _LL, _LL, _P, _LL, _P, _LL, _LL, c_int, c_int, c_int, c_int,
                                   _P, _LL, _P],
     "rllm_grouped_gemm_ragged": [c_int, c_int, _P, _LL, _P, _LL, _P, _LL, c_int, c_int, _P, _P, c_int, c_int, _P, _P, _P,
@@ -26,10 +26,12 @@ ops.register_signatures("mix", {
     "rllm_grouped_gemm_tc_supported": [_LL, c_int, c_int],
     "rllm_grouped_gemm_tc": [c_int, _P, _LL, _LL, _P, c_int, c_int, c_int, _P, _LL, _P, _P, c_int, _P, _P, _P, _P],
     "rllm_gather_rows_bf16": [_P, _LL, _P, _P, c_int, c_int, _P],
-    "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
+    "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
     "rllm_moe_plan": [_P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "rllm_rmsnorm_add": [_P, c_int, _P, _P, c_int, c_int, c_float, _P],
     "rllm_add_row": [_P, _P, c_int, c_int, _P],
+})
+ops.register_signatures("mix", {
     "rllm_latent_prepare": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_float, _P,
                             _P, _P, _P, _P],
     "rllm_latent_attention": [c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -71,7 +73,7 @@ def rmsnorm_add(residual: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: f
     parts = 1 if y.dim() == 2 else y.shape[1]
     _f32(y, "y", (T, H) if y.dim() == 2 else (T, parts, H))
     _f32(w, "w", (H,))
-    _check(_fn("mix", "rllm_rmsnorm_add")(y.data_ptr(), parts, w.data_ptr(), residual.data_ptr(), T, H, float(eps),
+    _check(_fn("experts", "rllm_rmsnorm_add")(y.data_ptr(), parts, w.data_ptr(), residual.data_ptr(), T, H, float(eps),
                                           _stream()), "rmsnorm_add")
     return residual
 
@@ -80,7 +82,7 @@ def add_row(h: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """h [T, H] += v [H] on every row, float32, in place."""
     _f32(h, "h")
     _f32(v, "v", (h.shape[1],))
-    _check(_fn("mix", "rllm_add_row")(h.data_ptr(), v.data_ptr(), h.shape[0], h.shape[1], _stream()), "add_row")
+    _check(_fn("experts", "rllm_add_row")(h.data_ptr(), v.data_ptr(), h.shape[0], h.shape[1], _stream()), "add_row")
     return h
 
 
@@ -104,7 +106,7 @@ def grouped_gemm_uniform(a: torch.Tensor, a_gs: int, w: torch.Tensor, out: torch
         _rows(gate, "gate", G)
         if gate.dtype != a.dtype or gate.shape[0] != a.shape[0]:
             raise KernelError("grouped product: the gate must have a's dtype and rows")
-    _check(_fn("mix", "rllm_grouped_gemm_uniform")(
+    _check(_fn("experts", "rllm_grouped_gemm_uniform")(
         _dt(a, "a"), epilogue, a.data_ptr(), a.stride(0), a_gs, w.data_ptr(), N * K, out.data_ptr(), out.stride(0),
         c_gs, a.shape[0], G, N, K, _ptr(gate), 0 if gate is None else gate.stride(0), _stream()), "grouped_gemm_uniform")
     return out
@@ -121,18 +123,24 @@ def tile_rows(dtype: torch.dtype, lda: int, K: int, n_rows: int = 1 << 30) -> in
     """Rows a plan's tile may have for a ragged product whose input has dtype `dtype`, row stride `lda` and
     depth K, over `n_rows` sorted rows: 128 where the tensor-core kernel takes it (32 for short lists), 64
     for the CUDA-core one. The products that share a plan must agree (take the smallest)."""
-    return _fn("mix", "rllm_grouped_gemm_tile_rows")(ops._DT[dtype], int(lda), int(K), int(min(n_rows, 1 << 30)))
+    return _fn("experts", "rllm_grouped_gemm_tile_rows")(ops._DT[dtype], int(lda), int(K), int(min(n_rows, 1 << 30)))
+
+
+SCORE_FNS = {"softmax": 0, "sigmoid": 1}
 
 
 def moe_topk(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
-             renorm: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
-    """(chosen experts int32 [T, top], their weights float32 [T, top]) from float32 router logits [T, E]."""
+             renorm: bool = False, score: str = "softmax") -> tuple[torch.Tensor, torch.Tensor]:
+    """(chosen experts int32 [T, top], their weights float32 [T, top]) from float32 router logits [T, E];
+    `score`: "softmax" over all experts, or "sigmoid" of each logit by itself."""
+    if score not in SCORE_FNS:
+        raise KernelError(f"router score {score!r} has no kernel (known: {sorted(SCORE_FNS)})")
     _f32(logits, "router logits")
     T, E = logits.shape
     idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     wt = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    _check(_fn("mix", "rllm_moe_topk")(logits.data_ptr(), T, E, int(groups), int(keep), int(top), int(bool(renorm)),
-                                       idx.data_ptr(), wt.data_ptr(), _stream()), "moe_topk")
+    _check(_fn("experts", "rllm_moe_topk")(logits.data_ptr(), T, E, int(groups), int(keep), int(top), int(bool(renorm)),
+                                           SCORE_FNS[score], idx.data_ptr(), wt.data_ptr(), _stream()), "moe_topk")
     return idx, wt
 
 
@@ -149,7 +157,7 @@ def moe_plan(idx: torch.Tensor, wt: torch.Tensor, experts: int, rows_per_tile: i
     p.rows_scale = torch.empty(n, dtype=torch.float32, device=dev)
     p.tiles = torch.empty(3 * p.max_tiles, dtype=torch.int32, device=dev)
     p.n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
-    _check(_fn("mix", "rllm_moe_plan")(idx.data_ptr(), wt.data_ptr(), T, top, experts, p.tile_rows, p.rows_tok.data_ptr(),
+    _check(_fn("experts", "rllm_moe_plan")(idx.data_ptr(), wt.data_ptr(), T, top, experts, p.tile_rows, p.rows_tok.data_ptr(),
                                        p.rows_dest.data_ptr(), p.rows_scale.data_ptr(), p.tiles.data_ptr(),
                                        p.n_tiles.data_ptr(), _stream()), "moe_plan")
     return p
@@ -170,7 +178,7 @@ def grouped_gemm_ragged(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: 
         raise KernelError(f"grouped product: out has dtype {out.dtype} and {out.shape[0]} rows")
     if not gather and a.shape[0] < plan.n_rows:
         raise KernelError("grouped product: a has fewer rows than the plan")
-    _check(_fn("mix", "rllm_grouped_gemm_ragged")(
+    _check(_fn("experts", "rllm_grouped_gemm_ragged")(
         _dt(a, "a"), epilogue, a.data_ptr(), a.stride(0), w.data_ptr(), N * K, out.data_ptr(), out.stride(0), N, K,
         plan.tiles.data_ptr(), plan.n_tiles.data_ptr(), plan.max_tiles, plan.tile_rows,
         plan.rows_tok.data_ptr() if gather else None,
@@ -181,7 +189,7 @@ def grouped_gemm_ragged(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: 
 
 def tc_supported(lda: int, N: int, K: int) -> bool:
     """Does the tcgen05 grouped product take a ragged product with these sizes (bfloat16, tiles of 128 rows)?"""
-    return bool(_fn("mix", "rllm_grouped_gemm_tc_supported")(int(lda), int(N), int(K)))
+    return bool(_fn("experts", "rllm_grouped_gemm_tc_supported")(int(lda), int(N), int(K)))
 
 
 def gather_rows_bf16(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
@@ -191,7 +199,7 @@ def gather_rows_bf16(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     if x.dtype != torch.bfloat16:
         raise KernelError("gather_rows_bf16 takes bfloat16 rows")
     out = torch.empty((idx.numel(), x.shape[1]), dtype=torch.bfloat16, device=x.device)
-    _check(_fn("mix", "rllm_gather_rows_bf16")(x.data_ptr(), x.stride(0), idx.data_ptr(), out.data_ptr(), idx.numel(),
+    _check(_fn("experts", "rllm_gather_rows_bf16")(x.data_ptr(), x.stride(0), idx.data_ptr(), out.data_ptr(), idx.numel(),
                                                x.shape[1], _stream()), "gather_rows_bf16")
     return out
 
@@ -211,7 +219,7 @@ def grouped_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: torc
         raise KernelError("tcgen05 grouped product: bfloat16 operands, a plan with tiles of 128 rows, relu^2 or float store")
     if out.dtype != (torch.float32 if epilogue == GEPI_STORE_F32 else torch.bfloat16) or out.shape[0] < plan.n_rows:
         raise KernelError(f"tcgen05 grouped product: out has dtype {out.dtype} and {out.shape[0]} rows")
-    _check(_fn("mix", "rllm_grouped_gemm_tc")(
+    _check(_fn("experts", "rllm_grouped_gemm_tc")(
         epilogue, a.data_ptr(), a.stride(0), plan.n_rows, w.data_ptr(), E, N, K, out.data_ptr(), out.stride(0),
         plan.tiles.data_ptr(), plan.n_tiles.data_ptr(), plan.max_tiles, plan.rows_dest.data_ptr() if scatter else None,
         plan.rows_scale.data_ptr() if scale else None, _ptr(err), _stream()), "grouped_gemm_tc")

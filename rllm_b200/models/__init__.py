@@ -1,5 +1,6 @@
 from .model import LayerCall, Model
 from . import llama  # registers LlamaForCausalLM
 from . import zukotar  # registers Zukotar
+from . import livovik  # registers Livovik
 
-__all__ = ["LayerCall", "Model", "llama", "zukotar"]
+__all__ = ["LayerCall", "Model", "llama", "zukotar", "livovik"]

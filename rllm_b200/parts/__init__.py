@@ -1,14 +1,14 @@
-from .base import (CacheKind, KVCacheSpec, LayerCache, Param, Part, Source, StateSpec, cache_kind_of,
+from .base import (CacheKind, KVCacheSpec, LayerCache, Param, Part, Source, StateSpec, Summands, cache_kind_of,
                    make_part, register_cache_kind, register_part, registered_parts)
 from .rope_rules import register_rope_rule, registered_rope_rules
 from .norm import RMSNorm
 from .rope import InterleavedRotary, RotaryEmbedding, inverse_frequencies
-from .attention import GQAttention
-from .ffn import SwiGLU
-from .block import LoopStep, PreNormBlock, SandwichBlock
+from .attention import GQAttention, SinkGQAttention
+from .ffn import ActFFN, SwiGLU
+from .block import LoopStep, PostNormBlock, PreNormBlock, SandwichBlock
 from .latent_attention import LatentAttention, LatentCacheSpec
 from .gla import GatedLinearAttention
-from .moe import RoutedExperts
+from .moe import GatedRoutedExperts, RoutedExperts
 from .embedding import Embedding, OutputHead
 
 __all__ = ["CacheKind", "cache_kind_of", "register_cache_kind", "register_rope_rule", "registered_rope_rules",
@@ -16,4 +16,5 @@ __all__ = ["CacheKind", "cache_kind_of", "register_cache_kind", "register_rope_r
            "register_part", "registered_parts", "RMSNorm", "RotaryEmbedding",
            "inverse_frequencies", "GQAttention", "SwiGLU", "PreNormBlock", "Embedding",
            "OutputHead", "InterleavedRotary", "SandwichBlock", "LoopStep", "LatentAttention",
-           "LatentCacheSpec", "GatedLinearAttention", "RoutedExperts"]
+           "LatentCacheSpec", "GatedLinearAttention", "RoutedExperts", "Summands", "SinkGQAttention", "ActFFN",
+           "PostNormBlock", "GatedRoutedExperts"]

@@ -68,3 +68,79 @@ class GQAttention(Part):
 
 
 register_part("mixer", "gqa", GQAttention)
+
+
+class SinkGQAttention(Part):
+    """Grouped-query attention with what some designs put around it, every piece a constructor argument:
+
+    * keys of `head_dim` and values of `v_dim` numbers per head;
+    * `qk_norm`: queries and keys divided by their root mean square per head, times a weight of `head_dim`
+      numbers shared by all heads (tensors `q.norm`, `k.norm`), before the rotation;
+    * `position`: a rotary part (its `rot_dim` leading dimensions of a head are rotated, the rest pass) or None;
+    * the mask: causal, and a `window` (the last `window` positions) and/or a `chunk` (only the positions of the
+      query's own block of `chunk` positions, blocks counted from position 0);
+    * `sink`: one learned number per head (tensor `sink`) whose exponential joins the softmax's denominator;
+    * `gate`: head h's output times sigmoid((W_g x)_h) (tensor `g`, one row per head), before W_o.
+
+    Scores, softmax, norms, rotation and the gate's sigmoid are float. `forward(..., residual=None)` returns
+    the float output (for blocks that norm after the sum). `names`: the checkpoint names of q, k, v, o."""
+    graph_safe = True
+    returns_output = True
+
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, v_dim: int | None = None,
+                 position: Part | None = None, scale: float | None = None, window: int | None = None,
+                 chunk: int | None = None, qk_norm: bool = False, sink: bool = False, gate: bool = False,
+                 eps: float = 1e-6, names=("q", "k", "v", "o")):
+        if heads % kv_heads:
+            raise ValueError(f"heads {heads} must be a multiple of kv_heads {kv_heads}")
+        v_dim = head_dim if v_dim is None else v_dim
+        if not 0 < head_dim <= 256 or not 0 < v_dim <= 256:
+            raise ValueError(f"head sizes {head_dim} / {v_dim} must lie in 1..256")
+        self.hidden, self.heads, self.kv_heads, self.head_dim, self.v_dim = hidden, heads, kv_heads, head_dim, v_dim
+        self.position, self.window, self.chunk = position, window, chunk
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        self.qk_norm, self.sink, self.gate, self.eps, self.names = qk_norm, sink, gate, float(eps), names
+        self.w_qkv = self.w_o = self.w_g = self.q_norm = self.k_norm = self.sinks = None
+
+    def children(self):
+        return [] if self.position is None else [self.position]
+
+    def params(self):
+        W, H, G, D, V = self.hidden, self.heads, self.kv_heads, self.head_dim, self.v_dim
+        q, k, v, o = self.names
+        ps = [Param("w_qkv", (Source(q, (H * D, W)), Source(k, (G * D, W)), Source(v, (G * V, W)))),
+              Param("w_o", (Source(o, (W, H * V)),))]
+        if self.qk_norm:
+            ps += [Param("q_norm", (Source(q + ".norm", (D,), init="norm"),), role="vector"),
+                   Param("k_norm", (Source(k + ".norm", (D,), init="norm"),), role="vector")]
+        if self.sink:
+            ps.append(Param("sinks", (Source("sink", (H,)),), role="vector"))
+        if self.gate:
+            ps.append(Param("w_g", (Source("g", (H, W)),)))
+        return ps
+
+    def cache_spec(self):
+        return KVCacheSpec(self.kv_heads, self.head_dim, self.window, self.chunk,
+                           None if self.v_dim == self.head_dim else self.v_dim)
+
+    def finalize(self, device, dtype):
+        f32 = lambda t: None if t is None else t.float().contiguous()
+        self._qn, self._kn, self._sinks = f32(self.q_norm), f32(self.k_norm), f32(self.sinks)
+
+    def forward(self, x, ctx, cache, residual=None):
+        be = ctx.backend
+        x = x.tensor() if hasattr(x, "tensor") else x
+        H, G, D, V = self.heads, self.kv_heads, self.head_dim, self.v_dim
+        proj = be.linear(x, self.w_qkv)                                  # [T, q | k | v]
+        gate = be.linear_f32(x, self.w_g) if self.gate else None         # float logits [T, H]
+        pos = self.position
+        be.qk_norm_rope_store(proj, 0, H * D, (H + G) * D, H, G, D, V, 0 if pos is None else pos.rot_dim,
+                              self._qn, self._kn, self.eps, None if pos is None else pos.table(ctx), cache)
+        att = be.sink_attention(proj[:, : H * D], cache, ctx, H, self.scale, self.window, self.chunk, self._sinks, gate)
+        if residual is None:
+            return be.linear_f32(att, self.w_o)
+        be.linear_residual(att, self.w_o, residual)
+        return None
+
+
+register_part("mixer", "gqa_sink", SinkGQAttention)

@@ -49,10 +49,15 @@ class Param:
 
 @dataclass(frozen=True)
 class KVCacheSpec:
-    """Paged keys and values: `window` None keeps every key, else only the last `window`."""
+    """Paged keys and values: `window` None keeps every key, else only the last `window`. `chunk`: a
+    query sees only the keys of its own block of `chunk` positions (blocks counted from position 0), so
+    the pages before the current block are given back. `v_dim`: size of a value head where it differs
+    from the key's `head_dim`."""
     kv_heads: int
     head_dim: int
     window: int | None = None
+    chunk: int | None = None
+    v_dim: int | None = None
 
 
 @dataclass(frozen=True)
@@ -99,6 +104,8 @@ class CacheKind:
     table of its own; `allocate(spec, num_pages, page_size, dtype, device)` returns one layer's
     tensors by name, each with the page as its first dimension. `window(spec)` is how many positions
     a query looks back (None: all; pages that lie wholly before it go back to the pool);
+    `chunk(spec)` is the size of the blocks of positions a query is confined to (None: no such rule; the
+    pages before the block of the next position go back to the pool);
     `num_pages(spec, default)` the size of the group's pool; `page_bytes(spec, page_size, dtype)`
     what one page of one layer costs (for sizing the pool from free memory).
     Kinds that are not paged get a slot per live request:
@@ -107,6 +114,7 @@ class CacheKind:
     paged: bool
     allocate: Callable[..., dict]
     window: Callable[[Any], int | None] = lambda spec: None
+    chunk: Callable[[Any], int | None] = lambda spec: None
     num_pages: Callable[[Any, int], int] = lambda spec, default: default
     page_bytes: Callable[[Any, int, torch.dtype], int] = lambda spec, page_size, dtype: 0
 
@@ -131,7 +139,8 @@ def cache_kind_of(spec) -> CacheKind:
 
 def _kv_allocate(spec, num_pages, page_size, dtype, device):
     shape = (num_pages, spec.kv_heads, page_size, spec.head_dim)
-    return {"k": torch.zeros(shape, dtype=dtype, device=device), "v": torch.zeros(shape, dtype=dtype, device=device)}
+    vshape = shape[:3] + (spec.v_dim or spec.head_dim,)
+    return {"k": torch.zeros(shape, dtype=dtype, device=device), "v": torch.zeros(vshape, dtype=dtype, device=device)}
 
 
 def _state_allocate(spec, max_requests, _page_size, _dtype, device):
@@ -140,8 +149,8 @@ def _state_allocate(spec, max_requests, _page_size, _dtype, device):
 
 
 register_cache_kind(KVCacheSpec, CacheKind(
-    paged=True, allocate=_kv_allocate, window=lambda spec: spec.window,
-    page_bytes=lambda spec, page_size, dtype: 2 * spec.kv_heads * spec.head_dim * page_size
+    paged=True, allocate=_kv_allocate, window=lambda spec: spec.window, chunk=lambda spec: spec.chunk,
+    page_bytes=lambda spec, page_size, dtype: spec.kv_heads * (spec.head_dim + (spec.v_dim or spec.head_dim)) * page_size
     * torch.empty((), dtype=dtype).element_size()))
 register_cache_kind(StateSpec, CacheKind(paged=False, allocate=_state_allocate))
 
@@ -170,6 +179,16 @@ def make_part(role: str, name: str, **kwargs) -> Part:
 
 def registered_parts(role: str) -> list[str]:
     return sorted(n for r, n in _KINDS if r == role)
+
+
+@dataclass
+class Summands:
+    """A sublayer's output in pieces, for a block whose norm kernel adds them itself: `parts` float
+    [T, n, hidden] (added in order), and optionally `extra` float [T, hidden] times the sigmoid of the first
+    column of `extra_gate` float [T, >= 1]."""
+    parts: torch.Tensor
+    extra: torch.Tensor | None = None
+    extra_gate: torch.Tensor | None = None
 
 
 @dataclass

@@ -2,7 +2,8 @@
 order (src/model/registry/llama.rs:163-245): h += mixer(norm(h)); h += ffn(norm(h)).
 `SandwichBlock` norms each sublayer's output as well: h += norm_b(mixer(norm(h))), the same for
 the feed-forward, which may be absent. `LoopStep` is a block that only adds a learned vector to
-every row: what a pass of a looped stretch of layers begins with."""
+every row: what a pass of a looped stretch of layers begins with. `PostNormBlock` norms after the sum,
+h = norm(alpha h + sublayer(h)), the sublayers reading the stream itself."""
 from __future__ import annotations
 
 from .base import Param, Part, Source, register_part
@@ -99,6 +100,55 @@ class SandwichBlock(Part):
         return y
 
 
+class PostNormBlock(Part):
+    """h <- norm1(alpha h + mixer(h)); h <- norm2(alpha h + ffn(h)) (the feed-forward may be absent). The
+    sublayers read the stream itself, in the run's storage type; sum and norm are one float kernel, which
+    also writes the copy that the next sublayer's products read. A feed-forward may return its output as
+    `Summands` (parts to be added in order, and a second summand with a sigmoid gate per row), which that
+    kernel takes as they come. `names`: checkpoint sub-prefixes of mixer and feed-forward; the norms'
+    weights are tensors named by each norm's `weight_name` under the block's prefix."""
+    graph_safe = True
+
+    def __init__(self, mixer: Part, mixer_norm: Part, ffn: Part | None = None, ffn_norm: Part | None = None,
+                 alpha: float = 1.0, names=("mix.", "mlp.")):
+        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = mixer, mixer_norm, ffn, ffn_norm
+        self.alpha, self.names = float(alpha), names
+
+    def children(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None]
+
+    def set_prefix(self, prefix: str):
+        self.prefix = prefix
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None:
+                norm.prefix = prefix
+        for part, sub in ((self.mixer, self.names[0]), (self.ffn, self.names[1])):
+            if part is not None:
+                if hasattr(part, "set_prefix"):
+                    part.set_prefix(prefix + sub)          # a part with named children of its own
+                    continue
+                part.prefix = prefix + sub
+                for c in part.children():
+                    if not c.prefix:
+                        c.prefix = part.prefix
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, h, ctx, cache):
+        """h: float32 residual stream [T, hidden], updated in place."""
+        be = ctx.backend
+        kept = ctx.per_forward.get("stream_copy")
+        x = kept[1] if kept is not None and kept[0] is h else be.stream_copy(h)
+        y = self.mixer.forward(x, ctx, cache, None)
+        x = be.postnorm(h, y, self.alpha, self.mixer_norm.weight_f32(), self.mixer_norm.eps)
+        if self.ffn is not None:
+            y = self.ffn.forward(x, ctx, None)
+            x = be.postnorm(h, y, self.alpha, self.ffn_norm.weight_f32(), self.ffn_norm.eps)
+        ctx.per_forward["stream_copy"] = (h, x)        # what the next block's mixer reads
+        return h
+
+
 class LoopStep(Part):
     """h += table[index] on every row. The passes of one loop share the table [times, hidden]: the
     first owns the tensor (`owner` None), the others name the first."""
@@ -126,4 +176,5 @@ class LoopStep(Part):
 
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "sandwich", SandwichBlock)
+register_part("block", "postnorm", PostNormBlock)
 register_part("block", "loop_step", LoopStep)

@@ -1,6 +1,8 @@
-"""SwiGLU feed-forward as a part: down(silu(gate x) * (up x)), added to the residual
-stream. Formula: src/gpu/cuda/shaders/moe.cu:141-146 and src/model/primitives.rs:557-585
-of the reference. Gate and up weights are stacked so that one product yields both."""
+"""Dense feed-forwards as parts. `SwiGLU`: down(silu(gate x) * (up x)). Formula:
+src/gpu/cuda/shaders/moe.cu:141-146 and src/model/primitives.rs:557-585 of the reference. Gate and up
+weights are stacked so that one product yields both. `ActFFN`: down(act(up x)) with act = relu(.)^2.
+Both add into the residual stream, or return their float output when `residual` is None (for blocks that
+norm after the sum)."""
 from __future__ import annotations
 
 from .base import Param, Part, Source, register_part
@@ -9,20 +11,50 @@ from .base import Param, Part, Source, register_part
 class SwiGLU(Part):
     graph_safe = True
     takes_deferred = True      # x goes to the backend's products as it comes
+    returns_output = True
 
-    def __init__(self, hidden: int, intermediate: int):
-        self.hidden, self.intermediate = hidden, intermediate
+    def __init__(self, hidden: int, intermediate: int,
+                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        self.hidden, self.intermediate, self.names = hidden, intermediate, names
         self.w_gate_up = self.w_down = None
 
     def params(self):
         H, I = self.hidden, self.intermediate
-        return [Param("w_gate_up", (Source("gate_proj.weight", (I, H)), Source("up_proj.weight", (I, H)))),
-                Param("w_down", (Source("down_proj.weight", (H, I)),))]
+        g, u, d = self.names
+        return [Param("w_gate_up", (Source(g, (I, H)), Source(u, (I, H)))),
+                Param("w_down", (Source(d, (H, I)),))]
 
     def forward(self, x, ctx, residual):
         be = ctx.backend
         act = be.linear_swiglu(x, self.w_gate_up)
+        if residual is None:
+            return be.linear_f32(act, self.w_down)
         be.linear_residual(act, self.w_down, residual)
 
 
+class ActFFN(Part):
+    """down(act(up x)), no biases; act: "relu2" = max(., 0)^2."""
+    graph_safe = True
+    returns_output = True
+    ACTS = ("relu2",)
+
+    def __init__(self, hidden: int, intermediate: int, act: str = "relu2", names=("up", "down")):
+        if act not in self.ACTS:
+            raise ValueError(f"activation {act!r} is not known (known: {self.ACTS})")
+        self.hidden, self.intermediate, self.act, self.names = hidden, intermediate, act, names
+        self.w_up = self.w_down = None
+
+    def params(self):
+        H, I = self.hidden, self.intermediate
+        return [Param("w_up", (Source(self.names[0], (I, H)),)), Param("w_down", (Source(self.names[1], (H, I)),))]
+
+    def forward(self, x, ctx, residual):
+        be = ctx.backend
+        a = be.linear_act(x, self.w_up, self.act)
+        if residual is None:
+            return be.linear_f32(a, self.w_down)
+        be.linear_residual(a, self.w_down, residual)
+
+
 register_part("ffn", "swiglu", SwiGLU)
+register_part("ffn", "act", ActFFN)

@@ -11,7 +11,7 @@ caller sums in slot order (`SandwichBlock` does it inside its norm).
 """
 from __future__ import annotations
 
-from .base import Param, Part, Source, register_part
+from .base import Param, Part, Source, Summands, register_part
 
 
 class RoutedExperts(Part):
@@ -45,4 +45,64 @@ class RoutedExperts(Part):
         return be.experts_down(be.experts_up(x, self._up, plan, self.act), self._down, plan, x.shape[0], self.top)
 
 
+class GatedRoutedExperts(Part):
+    """A mixture of gated experts: expert(h) = W_down (silu(W_gate h) * (W_up h)), no biases.
+
+    Router logits z = W_router h in float; scores by `score` ("sigmoid": each logit by itself; "softmax": over
+    all experts); the `top` largest scores are chosen and are the weights (`renorm`: divided by their sum).
+    The weight multiplies the expert's *input*: the output is the sum over the chosen experts of
+    expert(weight * h). Because gate and up projections are linear, the weight is applied to their float
+    results before the activation. `shared`: a dense gated feed-forward every token uses (its tensors under
+    `shared.`), added times sigmoid(W_sg h) (`shared.sg`, one row) when `shared_gate`. Returns `Summands`: one
+    float row per (token, chosen expert), the shared expert's output and its gate logit; the block's norm
+    kernel adds them."""
+    graph_safe = True
+    returns_output = True
+
+    def __init__(self, hidden: int, ff: int, experts: int, top: int, score: str = "sigmoid", renorm: bool = False,
+                 shared: Part | None = None, shared_gate: bool = False):
+        if top > experts:
+            raise ValueError(f"top {top} exceeds the {experts} experts")
+        self.hidden, self.ff, self.experts, self.top = hidden, ff, experts, top
+        self.score, self.renorm, self.shared, self.shared_gate = score, renorm, shared, shared_gate and shared is not None
+        self.w_router = self.w_gate_up = self.w_down = self.w_sg = None
+
+    def children(self):
+        return [] if self.shared is None else [self.shared]
+
+    def set_prefix(self, prefix: str):
+        self.prefix = prefix
+        if self.shared is not None:
+            self.shared.prefix = prefix + "shared."
+
+    def params(self):
+        E, W, F = self.experts, self.hidden, self.ff
+        ps = [Param("w_router", (Source("router", (E, W)),)),
+              Param("w_gate_up", tuple(Source(f"e{e}.{n}", (F, W)) for e in range(E) for n in ("gate", "up"))),
+              Param("w_down", tuple(Source(f"e{e}.down", (W, F)) for e in range(E)))]
+        if self.shared_gate:
+            ps.append(Param("w_sg", (Source("shared.sg", (1, W)),)))
+        return ps
+
+    def finalize(self, device, dtype):
+        self._gate_up = self.w_gate_up.view(self.experts, 2 * self.ff, self.hidden)
+        self._down = self.w_down.view(self.experts, self.hidden, self.ff)
+
+    def forward(self, x, ctx, residual=None):
+        if residual is not None:
+            raise NotImplementedError("GatedRoutedExperts returns its summands; the block adds them")
+        be = ctx.backend
+        x = x.tensor() if hasattr(x, "tensor") else x
+        T = x.shape[0]
+        _, _, plan = be.route(be.linear_f32(x, self.w_router), self.top, renorm=self.renorm, score=self.score,
+                              tile_rows=be.expert_tile_rows(x, self._gate_up, self._down, T * self.top))
+        act = be.experts_gated_up(x, self._gate_up, plan)             # silu(w g) * (w u), sorted rows
+        parts = be.experts_down(act, self._down, plan, T, self.top, scale=False)
+        if self.shared is None:
+            return Summands(parts)
+        return Summands(parts, self.shared.forward(x, ctx, None),
+                        be.linear_f32(x, self.w_sg) if self.shared_gate else None)
+
+
 register_part("ffn", "moe", RoutedExperts)
+register_part("ffn", "moe_gated", GatedRoutedExperts)

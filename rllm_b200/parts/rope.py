@@ -42,6 +42,10 @@ class RotaryEmbedding(Part):
         f = inverse_frequencies(self.rot_dim, self.theta, self.scaling)
         self.inv_freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
 
+    def table(self, ctx):
+        """float32 [T, rot_dim/2, 2] (cos, sin) for the step's tokens, shared by the layers of one rule."""
+        return ctx.backend.rope_table(ctx, ctx.positions, self.inv_freq, self.rot_dim, self.table_key)
+
     def project_rotate_store(self, x, w_qkv, bias, ctx, cache, nh, nkv):
         """qkv = x w_qkv^T (+ bias) with q and k rotated and k, v written into the layer's pages:
         the projection and this part's work in one kernel where the backend can."""
