@@ -7,11 +7,47 @@ tensor with the design's tensor names (`embed`, `l<i>.norm1`, `l<i>.mix.q`, ...,
 """
 from __future__ import annotations
 
+import json
 import math
+import os
+import struct
 
+import numpy as np
 import torch
 
 F64 = torch.float64
+DT = F64
+
+
+def read_safetensors(path):
+    """name -> float64 tensor (integer tables stay integers): 8-byte length, JSON header, raw bytes."""
+    with open(path, "rb") as f:
+        n = struct.unpack("<Q", f.read(8))[0]
+        header = json.loads(f.read(n))
+        data = f.read()
+    out = {}
+    for name, e in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = e["data_offsets"]
+        raw = data[a:b]
+        if e["dtype"] == "BF16":
+            bits = np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16
+            t = torch.from_numpy(bits.view(np.float32).copy()).to(F64)
+        elif e["dtype"] == "F32":
+            t = torch.from_numpy(np.frombuffer(raw, dtype="<f4").copy()).to(F64)
+        elif e["dtype"] == "I32":
+            t = torch.from_numpy(np.frombuffer(raw, dtype="<i4").copy())
+        else:
+            raise ValueError(f"{name}: dtype {e['dtype']}")
+        out[name] = t.reshape(e["shape"])
+    return out
+
+
+def read_model_dir(d):
+    with open(os.path.join(d, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, read_safetensors(os.path.join(d, "model.safetensors"))
 
 
 def rms_norm(x, w, eps):
@@ -140,7 +176,9 @@ def layer_forward(x, cfg, weights, i, positions=None):
     """x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ff(x)); a layer with `weights_of` j runs on
     layer j's tensors."""
     L = cfg["layers"][i]
-    src = L.get("weights_of", i) if L.get("weights_of") is not None else i
+    src = i
+    while cfg["layers"][src].get("weights_of") is not None:       # the layer that owns the tensors
+        src = cfg["layers"][src]["weights_of"]
     eps, alpha = float(cfg["norm"]["eps"]), float(cfg["postln_alpha"])
     pre = f"l{src}."
     if L["type"] != "attention":
