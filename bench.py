@@ -139,8 +139,33 @@ def _moe(ff, experts, top, groups, keep):
                                                             "groups": {"count": groups, "keep": keep}}}
 
 
+def _livovik_sizes():
+    """Four layers (dense feed-forward, then a routed one with a shared expert, then two more runs on the routed
+    layer's tensors), grouped-query heads like the Llama layers beside them, a block mask longer than every
+    context here so that both designs attend the same keys, feed-forwards with the Llama layers' active weights."""
+    out = {}
+    # width, heads, kv heads, head size | dense ff, experts, top, expert ff, shared ff | llama intermediate
+    for name, W, H, G, D, ff, E, top, eff, sff, inter in (
+            ("w2048", 2048, 32, 8, 64, 12288, 16, 4, 1536, 2048, 8192),
+            ("w4096", 4096, 32, 8, 128, 21504, 32, 6, 1792, 3584, 14336)):
+        mixer = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": 8192},
+                 "rot": {"base": 500000.0, "dims": D // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+        moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}, "shared": {"ff": sff}}
+        lv = {"architecture": "Livovik", "vocab": 32000, "width": W, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+              "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}},
+                         {"type": "attention", "mixer": mixer, "mlp": moe},
+                         {"type": "attention", "mixer": mixer, "mlp": moe, "weights_of": 1},
+                         {"type": "attention", "mixer": mixer, "mlp": moe, "weights_of": 1}]}
+        ll = dict(LLAMA_1B, hidden_size=W, num_hidden_layers=4, num_attention_heads=H, num_key_value_heads=G,
+                  head_dim=D, intermediate_size=inter, vocab_size=32000)
+        out[name] = (lv, ll)
+    return out
+
+
 def design_sizes(design):
     """name -> (the design's configuration, Llama layers of equal width, depth and active feed-forward weights)."""
+    if design == "livovik":
+        return _livovik_sizes()
     assert design == "zukotar"
     out = {}
     # width, heads, latent rank, experts, top, expert ff, groups, keep | llama heads, kv heads, head size, intermediate
@@ -239,7 +264,7 @@ def main():
     ap.add_argument("--workloads", default="", help="comma-separated: mixed_3b, continuous_8b, or all")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (for profiling; the JSON line then lacks the other parts)")
-    ap.add_argument("--designs", default="", choices=["", "zukotar"],
+    ap.add_argument("--designs", default="", choices=["", "zukotar", "livovik"],
                     help="instead of the default workload: prefill and decode of this design beside Llama layers of "
                          "equal size (random weights), with the time per operation; prints its own JSON line")
     ap.add_argument("--profile-range", action="store_true",

@@ -54,7 +54,25 @@ struct DecParams {
   int nh, nkv, page_size, window, splits;
   int page_shift;       // log2(page_size), or -1 when it is no power of two
   float scale_log2e;
+  int chunk;            // > 0: the token sees only the keys of its own block of this many positions
+  const float* sinks;   // per head, or null: exp(sink) joins the denominator (no key, no value)
+  const float* gate;    // float logits [S, gate_ld] or null: head h's output times sigmoid(gate[seq, h])
+  int gate_ld;
 };
+
+// The last step of a row: the sink joins the denominator, the sum is divided, the gate applied.
+__device__ __forceinline__ float finish_row(const DecParams& p, float O, float L, float M, int seq, int head) {
+  if (p.sinks) {
+    const float sk = p.sinks[head] * 1.4426950408889634f;
+    const float M2 = fmaxf(M, sk);
+    const float f = (M == -INFINITY) ? 0.f : exp2f(M - M2);
+    L = L * f + exp2f(sk - M2);
+    O *= f;
+  }
+  float inv = L > 0.f ? 1.f / L : 0.f;
+  if (p.gate) inv *= 1.f / (1.f + __expf(-p.gate[(size_t)seq * p.gate_ld + head]));
+  return O * inv;
+}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -144,7 +162,8 @@ attn_decode_kernel(const DecParams p) {
   // the kernel before this one, so they may be read before the wait
   const int kv_len = p.kv_lens[seq];
   const int pos = kv_len - 1;
-  const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  if (p.chunk > 0) lo = max(lo, pos / p.chunk * p.chunk);
   const int tile_first = lo / TILE;
   const int tiles_total = pos / TILE + 1 - tile_first;
   const int per = (tiles_total + p.splits - 1) / p.splits;
@@ -335,8 +354,8 @@ attn_decode_kernel(const DecParams p) {
       O += w_o[((size_t)w * G + r) * HD + d] * f;
     }
     if (p.splits == 1) {
-      const float inv = L > 0.f ? 1.f / L : 0.f;
-      p.out[(size_t)seq * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(O * inv);
+      p.out[(size_t)seq * p.out_stride + (size_t)(kvh * G + r) * HD + d] =
+          __float2bfloat16_rn(finish_row(p, O, L, M, seq, kvh * G + r));
     } else {
       c_o[r * HD + d] = O;
       if (d == 0) { c_m[r] = M; c_l[r] = L; }
@@ -375,8 +394,8 @@ attn_decode_kernel(const DecParams p) {
             O += ld_cluster_f32(bo[s] + (uint32_t)(r * HD + d) * 4) * f;
           }
         }
-        const float inv = L > 0.f ? 1.f / L : 0.f;
-        p.out[(size_t)seq * p.out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(O * inv);
+        p.out[(size_t)seq * p.out_stride + (size_t)(kvh * G + r) * HD + d] =
+            __float2bfloat16_rn(finish_row(p, O, L, M, seq, kvh * G + r));
       }
     }
     __syncwarp();
@@ -418,11 +437,14 @@ int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
 // q: [S, ...] bf16, one row per sequence, stride q_stride, head h at h*hd; out likewise.
 // kcache / vcache: [num_pages][nkv][page_size][hd] bf16. kv_lens [S]: keys visible to each
 // sequence's token (its own included). splits: ranges of keys per sequence (1..16, one cluster).
+// chunk > 0: only the keys of the token's own block of `chunk` positions; sinks float [nh] or null; gate float
+// logits [S, gate_ld] or null (see DecParams).
 // `err` is not used (this kernel has no wait that can run out); it keeps the launchers alike.
 RLLM_API int rllm_attention_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
                                    long long num_pages, void* out, int out_stride, const int* kv_lens,
                                    const int* block_table, int bt_stride, int num_seqs, int nh, int nkv, int hd,
-                                   int page_size, float scale, int window, int splits, int* err, void* stream) {
+                                   int page_size, float scale, int window, int chunk, const float* sinks,
+                                   const float* gate, int gate_ld, int splits, int* err, void* stream) {
   (void)err;
   if (num_seqs <= 0) return 0;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 16) return ERR_BAD_SIZE;
@@ -434,6 +456,7 @@ RLLM_API int rllm_attention_decode(const void* q, int q_stride, const void* kcac
   p.out = (bf16*)out; p.out_stride = out_stride;
   p.kv_lens = kv_lens; p.block_table = block_table; p.bt_stride = bt_stride; p.nh = nh; p.nkv = nkv;
   p.page_size = page_size; p.window = window; p.splits = splits; p.scale_log2e = scale * 1.4426950408889634f;
+  p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_ld = gate_ld;
   p.page_shift = -1;
   for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) p.page_shift = sft;
   cudaStream_t s = (cudaStream_t)stream;

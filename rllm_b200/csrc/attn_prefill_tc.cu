@@ -87,6 +87,10 @@ struct PfParams {
   bf16* out; int out_stride;
   const int* cu_q; const int* kv_lens; const int* block_table; int bt_stride;
   int nh, nkv, page_size, page_shift, window;
+  int chunk;             // > 0: a row sees only the keys of its own block of this many positions
+  const float* sinks;    // per head, or null: exp(sink) joins a row's denominator (no key, no value)
+  const float* gate;     // float logits [T, gate_ld] or null: head h's output times sigmoid(gate[t, h])
+  int gate_ld;
   int box_rows;          // TMA variant: keys per copy = min(page size, 128)
   int row_pairs, num_seqs, sm_count;
   float scale_log2e;
@@ -189,7 +193,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   int kv_begin = 0, n_t[RT];
   {
     const int p_min = kv_len - q_len + (tile0 * PM) / G;
-    if (p.window > 0 && p_min - p.window + 1 > 0) kv_begin = (p_min - p.window + 1) / PN * PN;
+    int first = (p.window > 0 && p_min - p.window + 1 > 0) ? p_min - p.window + 1 : 0;
+    if (p.chunk > 0) first = max(first, p_min / p.chunk * p.chunk);
+    kv_begin = first / PN * PN;
 #pragma unroll
     for (int g = 0; g < RT; ++g) {
       const bool active = (tile0 + g) * PM < rows_total;         // uniform: a row tile beyond the sequence's rows is empty
@@ -390,7 +396,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const bool valid = row < rows_total;
     const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
     const int pos = kv_len - q_len + tok;
-    const int lo = p.window > 0 ? pos - p.window + 1 : 0;
+    int lo = p.window > 0 ? pos - p.window + 1 : 0;
+    if (p.chunk > 0) lo = max(lo, pos / p.chunk * p.chunk);
     if (TMA) {
       // this thread's own row of Q into the A-operand layout (rows beyond the sequence zero), while the
       // first K and V tiles are on their way
@@ -412,7 +419,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const uint32_t prow = p_s + (uint32_t)g * C::P_BYTES + (uint32_t)(r * 128);
     constexpr int NC = PN / 32;                           // the row's scores come 32 at a time
     const float sl = p.scale_log2e;
-    float m = -INFINITY, l = 0.f;       // m: what the exponentials are taken against, up to 2^8 behind the true maximum
+    // m: what the exponentials are taken against, up to 2^8 behind the true maximum. A sink opens the row's
+    // running softmax as a key of score `sink` (not scaled) and value zero.
+    const bool sunk = p.sinks != nullptr && valid;
+    float m = sunk ? p.sinks[head] * 1.4426950408889634f : -INFINITY, l = sunk ? 1.f : 0.f;
     bool ok = true;
 
     auto wait_on = [&](uint64_t* bar, uint32_t parity, int role, int t) -> bool {
@@ -505,7 +515,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     }
     if (ok && wait_on(&pv_full[g], (uint32_t)(n_mine - 1) & 1u, 25, n_mine)) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      if (p.gate && valid) inv *= 1.f / (1.f + __expf(-p.gate[(size_t)(q0 + tok) * p.gate_ld + head]));
       bf16* dst = p.out + (size_t)(q0 + tok) * p.out_stride + (size_t)head * HD;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
@@ -605,11 +616,14 @@ int launch_pf(const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, i
 // q: [T, ...] bf16 rows with stride q_stride, head h at h*hd; out likewise (16-byte aligned rows).
 // kcache / vcache: [num_pages][nkv][page_size][hd] bf16. cu_q [S+1], kv_lens [S], block_table [S, bt_stride].
 // max_q_len: the longest portion in the batch (sizes the list of work items). Head sizes 64 and 128.
+// chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks counted from position 0);
+// sinks: float [nh] or null; gate: float logits [T, gate_ld] or null (see PfParams).
 // sm_count: CTAs to launch at most (0: asked from the device).
 RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* kcache, const void* vcache,
                                        void* out, int out_stride, const int* cu_q, const int* kv_lens,
                                        const int* block_table, int bt_stride, int num_seqs, int max_q_len,
                                        int num_pages, int nh, int nkv, int hd, int page_size, float scale, int window,
+                                       int chunk, const float* sinks, const float* gate, int gate_ld,
                                        int* err, int sm_count, void* stream) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0) return ERR_BAD_SIZE;
@@ -621,6 +635,7 @@ RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* 
   p.block_table = block_table; p.bt_stride = bt_stride; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
   p.page_shift = -1;
   if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
+  p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_ld = gate_ld;
   p.window = window; p.scale_log2e = scale * 1.4426950408889634f; p.err = err;
   const int G = nh / nkv;
   p.row_pairs = (max_q_len * G + RT * PM - 1) / (RT * PM); p.num_seqs = num_seqs;

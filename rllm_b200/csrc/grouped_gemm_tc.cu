@@ -24,7 +24,7 @@ namespace {
 constexpr int TM = 128, TN = 128, TK = 64, UK = 16, STAGES = 3;
 constexpr int OPERAND_BYTES = TM * TK * 2, STAGE_BYTES = 2 * OPERAND_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
-enum : int { TEPI_RELU2 = 2, TEPI_F32 = 1 };
+enum : int { TEPI_RELU2 = 2, TEPI_F32 = 1, TEPI_SILU_GATED = 3 };
 
 struct TcArgs {
   void* C; long long ldc;
@@ -137,6 +137,23 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             if (n + j < p.N)                    // N is a multiple of 8: four are in or out together
               *reinterpret_cast<float4*>(c + j) = make_float4(__uint_as_float(v[j]) * f, __uint_as_float(v[j + 1]) * f,
                                                               __uint_as_float(v[j + 2]) * f, __uint_as_float(v[j + 3]) * f);
+        } else if (EPI == TEPI_SILU_GATED) {
+          // the weight's rows come in blocks of 16 gate rows followed by their 16 up rows: these 32 columns hold
+          // both halves of 16 outputs. The row's weight scales both linear results before the activation.
+          if (n >= p.N) continue;                 // N is a multiple of 32
+          bf16* c = (bf16*)p.C + crow * p.ldc + n / 2;
+#pragma unroll
+          for (int j = 0; j < 16; j += 8) {
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float g0 = __uint_as_float(v[j + 2 * q]) * f, g1 = __uint_as_float(v[j + 2 * q + 1]) * f;
+              const float u0 = __uint_as_float(v[16 + j + 2 * q]) * f, u1 = __uint_as_float(v[16 + j + 2 * q + 1]) * f;
+              __nv_bfloat162 h = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+              o[q] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(c + j) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
         } else {
           bf16* c = (bf16*)p.C + crow * p.ldc + n;
 #pragma unroll
@@ -223,7 +240,8 @@ RLLM_API int rllm_grouped_gemm_tc_supported(long long lda, int N, int K) {
 
 // A: bfloat16 [a_rows, K], row stride lda: the plan's sorted rows. W: bfloat16 [E, N, K]. The plan (tiles of up to 128
 // rows) as for rllm_grouped_gemm_ragged. epi 2: C bfloat16 [a_rows, N] = relu(.)^2 in sorted order; epi 1: C float,
-// row rows_out[r] = row_scale[r] * (.). err: one int on the device for a wait that ran out, or null.
+// row rows_out[r] = row_scale[r] * (.); epi 3: W's rows in blocks of 16 gate rows and their 16 up rows (N a multiple
+// of 32), C bfloat16 [a_rows, N / 2] = silu(f g) * (f u) with f = row_scale[r]. err: one int on the device for a wait that ran out, or null.
 RLLM_API int rllm_grouped_gemm_tc(int epi, const void* A, long long lda, long long a_rows, const void* W, int E, int N,
                                   int K, void* C, long long ldc, const int* tiles, const int* n_tiles, int max_tiles,
                                   const int* rows_out, const float* row_scale, int* err, void* stream) {
@@ -238,6 +256,10 @@ RLLM_API int rllm_grouped_gemm_tc(int epi, const void* A, long long lda, long lo
   dim3 grid((N + TN - 1) / TN, max_tiles, 1);
   if (epi == TEPI_RELU2) return launch_tc<TEPI_RELU2>(ma, mw, p, grid, (cudaStream_t)stream);
   if (epi == TEPI_F32) return launch_tc<TEPI_F32>(ma, mw, p, grid, (cudaStream_t)stream);
+  if (epi == TEPI_SILU_GATED) {
+    if (N % 32) return ERR_BAD_SIZE;
+    return launch_tc<TEPI_SILU_GATED>(ma, mw, p, grid, (cudaStream_t)stream);
+  }
   return ERR_BAD_SIZE;
 }
 

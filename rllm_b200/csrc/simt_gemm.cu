@@ -108,7 +108,56 @@ int launch(int epi, const void* A, const void* W, void* C, const void* bias, int
   return rc;
 }
 
+// Few outputs a row (a gate row, a handful of heads or experts): one warp a row of A, the lanes stride over K
+// and keep one sum per output; a row's sums are added in one fixed order whatever else the batch holds.
+constexpr int SKINNY_MAX = 8;
+
+template <typename TI>
+__global__ void __launch_bounds__(128)
+gemm_skinny_kernel(const TI* __restrict__ A, const TI* __restrict__ W, float* __restrict__ C, int T, int N, int K,
+                   long long lda, int ldc) {
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  const TI* a = A + t * lda;
+  float acc[SKINNY_MAX];
+#pragma unroll
+  for (int n = 0; n < SKINNY_MAX; ++n) acc[n] = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float x = to_f32(a[k]);
+#pragma unroll
+    for (int n = 0; n < SKINNY_MAX; ++n)
+      if (n < N) acc[n] = fmaf(x, to_f32(W[(size_t)n * K + k]), acc[n]);
+  }
+#pragma unroll
+  for (int n = 0; n < SKINNY_MAX; ++n) {
+    if (n < N) {
+      const float v = warp_sum(acc[n]);
+      if (lane == 0) C[t * ldc + n] = v;
+    }
+  }
+}
+
 }  // namespace
+
+// C[T, N] (float, row stride ldc) = A[T, K] (row stride lda) W[N, K]^T for N <= 8.
+RLLM_API int rllm_gemm_skinny(int dt, const void* A, const void* W, float* C, int T, int N, int K, long long lda,
+                              int ldc, void* stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || N > SKINNY_MAX) return ERR_BAD_SIZE;
+  const long long blocks = ((long long)T + 3) / 4;
+  if (blocks > 2147483647LL) return ERR_TOO_LARGE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dt == DT_F32)
+    return launch_ex(gemm_skinny_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (const float*)A,
+                     (const float*)W, C, T, N, K, lda, ldc);
+  if (dt == DT_BF16)
+    return launch_ex(gemm_skinny_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (const bf16*)A,
+                     (const bf16*)W, C, T, N, K, lda, ldc);
+  return ERR_BAD_DTYPE;
+}
 
 // A: [T, K] with row stride lda; W: [N, K] ([2N, K] for the SwiGLU epilogue);
 // C: [T, N] with row stride ldc, of the type the epilogue names; bias [N] or null.

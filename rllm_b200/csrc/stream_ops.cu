@@ -5,8 +5,9 @@
 //            float throughout, the parts added in order. Also writes h[t] in the run's storage type (`copy`),
 //            which is what the next sublayer's products read.
 // cast_rows: the stream in the run's storage type (the first layer's input).
-// gated_act: out[r, i] = act(scale_r * gu[r, i]) * (scale_r * gu[r, F + i]) for gu [R, 2F] (float or storage type),
-//            act = silu. relu2: x <- max(x, 0)^2 in place.
+// gated_act: out[r, i] = act(scale_r * g) * (scale_r * u) for gu [R, 2F] (float or storage type), act = silu; the
+//            columns of gu come in blocks of `block` gate columns followed by their up columns (block = F: all gate
+//            columns, then all up columns). relu2: x <- max(x, 0)^2 in place.
 #include "common.cuh"
 using namespace rllm;
 
@@ -51,15 +52,16 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, bf16* __restrict__
 }
 
 template <typename TI, typename TO>
-__global__ void gated_act_kernel(const TI* __restrict__ gu, long long ld, TO* __restrict__ out, int F, long long n,
-                                 const float* __restrict__ row_scale) {
+__global__ void gated_act_kernel(const TI* __restrict__ gu, long long ld, TO* __restrict__ out, int F, int block,
+                                 long long n, const float* __restrict__ row_scale) {
   pdl_launch();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F;
     const int c = (int)(i % F);
     const float f = row_scale ? row_scale[r] : 1.f;
-    const float g = f * to_f32(gu[r * ld + c]), u = f * to_f32(gu[r * ld + F + c]);
+    const long long at = r * ld + (long long)(c / block) * 2 * block + c % block;     // blocks of gate columns, then their up columns
+    const float g = f * to_f32(gu[at]), u = f * to_f32(gu[at + block]);
     out[i] = from_f32<TO>(g / (1.f + expf(-g)) * u);
   }
 }
@@ -106,18 +108,19 @@ RLLM_API int rllm_cast_rows(const float* x, void* out, long long n, void* stream
 }
 
 // gu [R, >= 2F] of type in_dt with row stride ld -> out [R, F] of type out_dt; row_scale float [R] or null.
-RLLM_API int rllm_gated_act(const void* gu, int in_dt, long long ld, void* out, int out_dt, int R, int F,
+RLLM_API int rllm_gated_act(const void* gu, int in_dt, long long ld, void* out, int out_dt, int R, int F, int block,
                             const float* row_scale, void* stream) {
   if (R <= 0 || F <= 0) return 0;
+  if (block <= 0 || F % block) return ERR_BAD_SIZE;
   const long long n = (long long)R * F;
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 g(blocks_for(n)), b(256);
   if (in_dt == DT_F32 && out_dt == DT_F32)
-    return launch_ex(gated_act_kernel<float, float>, g, b, 0, s, 1, (const float*)gu, ld, (float*)out, F, n, row_scale);
+    return launch_ex(gated_act_kernel<float, float>, g, b, 0, s, 1, (const float*)gu, ld, (float*)out, F, block, n, row_scale);
   if (in_dt == DT_F32 && out_dt == DT_BF16)
-    return launch_ex(gated_act_kernel<float, bf16>, g, b, 0, s, 1, (const float*)gu, ld, (bf16*)out, F, n, row_scale);
+    return launch_ex(gated_act_kernel<float, bf16>, g, b, 0, s, 1, (const float*)gu, ld, (bf16*)out, F, block, n, row_scale);
   if (in_dt == DT_BF16 && out_dt == DT_BF16)
-    return launch_ex(gated_act_kernel<bf16, bf16>, g, b, 0, s, 1, (const bf16*)gu, ld, (bf16*)out, F, n, row_scale);
+    return launch_ex(gated_act_kernel<bf16, bf16>, g, b, 0, s, 1, (const bf16*)gu, ld, (bf16*)out, F, block, n, row_scale);
   return ERR_BAD_DTYPE;
 }
 

@@ -92,7 +92,8 @@ class Backend:
         # weights whose height is no multiple of 4 (a gate row per head, say) stay on the CUDA cores
         return self._sm100 is not None and w.shape[0] % 4 == 0 and self._sm100.gemm_supported(x, w)
 
-    def linear(self, x, w, bias=None):
+    def linear(self, x, w, bias=None, tag=None):
+        # `tag` names the product for per-operation timing (kernels/profile.py); it changes nothing here
         if bias is None and self._fused_norm(x, w):
             return self._sm100.gemm_norm(x.h, x.weight, x.eps, w, ops.EPI_STORE, rows=x.rows)
         x = x.tensor() if isinstance(x, Normed) else x
@@ -102,7 +103,9 @@ class Backend:
             return y if bias is None else ops.add_bias(y, bias)
         return ops.gemm_simt(x, w, ops.EPI_STORE, bias=bias)
 
-    def linear_f32(self, x, w):
+    def linear_f32(self, x, w, tag=None):
+        if w.shape[0] <= ops.SKINNY_MAX:         # a gate row, a handful of heads: a warp a token
+            return ops.gemm_skinny(x.tensor() if isinstance(x, Normed) else x, w)
         if self._fused_norm(x, w):
             return self._sm100.gemm_norm(x.h, x.weight, x.eps, w, ops.EPI_STORE_F32, rows=x.rows)
         x = x.tensor() if isinstance(x, Normed) else x
@@ -224,20 +227,25 @@ class Backend:
                                              err=self._sm100.init(self.device).err)
         return self._mix.grouped_gemm_ragged(x, w_up, plan, out, self._mix.GEPI_RELU2, gather=True)
 
-    def experts_gated_up(self, x, w_gate_up, plan):
-        """silu(f g) * (f u) for every sorted row of the plan, with [g | u] = x[token of row] W[expert of row]^T
-        (W [E, 2F, K]: an expert's gate rows, then its up rows) and f the row's weight: the weight on the
-        expert's input, applied in float to the two linear projections."""
+    def experts_gated_up(self, x, w_gate_up, plan, block=None):
+        """silu(f g) * (f u) for every sorted row of the plan, with g and u the row's token times the gate and up
+        rows of the row's expert and f the row's weight: the weight on the expert's input, applied in float to the
+        two linear projections. W [E, 2F, K]: an expert's gate rows, then its up rows (`block` None), or blocks of
+        `block` gate rows each followed by their up rows (16: the tcgen05 kernel then activates in its epilogue)."""
         F2 = w_gate_up.shape[1]
         if self._tc_experts(x, w_gate_up, plan):
             rows = self._mix.gather_rows_bf16(x, plan.rows_tok)
+            if block == 16:
+                out = torch.empty((plan.n_rows, F2 // 2), dtype=torch.bfloat16, device=x.device)
+                return self._mix.grouped_gemm_tc(rows, w_gate_up, plan, out, self._mix.GEPI_SILU_GATED, scale=True,
+                                                 err=self._sm100.init(self.device).err)
             gu = torch.empty((plan.n_rows, F2), dtype=torch.float32, device=x.device)
             self._mix.grouped_gemm_tc(rows, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32,
                                       err=self._sm100.init(self.device).err)
         else:
             gu = torch.empty((plan.n_rows, F2), dtype=torch.float32, device=x.device)
             self._mix.grouped_gemm_ragged(x, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32, gather=True)
-        return self._sink.gated_act(gu, x.dtype, plan.rows_scale)
+        return self._sink.gated_act(gu, x.dtype, plan.rows_scale, block)
 
     def experts_down(self, a, w_down, plan, T, top, scale=True):
         """(weight of row, if `scale`) * (a[row] W_down[expert of row]^T), stored at the row's (token, slot):
@@ -272,7 +280,7 @@ class Backend:
         """act(x W^T) in the run dtype; act "relu2" = max(., 0)^2."""
         if act != "relu2":
             raise ops.KernelError(f"activation {act!r} has no kernel")
-        return self._sink.relu2_(self.linear(x, w))
+        return self._sink.relu2_(self.linear(x, w, tag="up"))
 
     def qk_norm_rope_store(self, proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table, cache):
         writes = cache.writes
@@ -285,21 +293,34 @@ class Backend:
         may differ in size: bfloat16 on the tensor cores where the kernel takes the sizes, else (and in the
         32-bit run) in float on the CUDA cores."""
         sk = self._sink
-        kd, vd = cache.k.shape[3], cache.v.shape[3]
-        if self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1" and \
-                sk.mma_supported(q.dtype, kd, vd, cache.page_size):
-            # keys a query of this step can see at most, known without a device read (graph captures included)
-            keys = ctx.max_kv_len
-            if window:
-                keys = min(keys, window + ctx.max_q_len)
-            if chunk:
-                keys = min(keys, chunk)
-            G = nh // cache.k.shape[1]
+        kd, vd, nkv = cache.k.shape[3], cache.v.shape[3], cache.k.shape[1]
+        tc = self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1"
+        # keys a query of this step can see at most, known without a device read (graph captures included)
+        keys = ctx.max_kv_len
+        if window:
+            keys = min(keys, window + ctx.max_q_len)
+        if chunk:
+            keys = min(keys, chunk)
+        G = nh // nkv
+        if tc and kd == vd and self._sm100.attention_supported(q, cache.k):
+            # equal head sizes of 64 or 128: the kernels of plain grouped-query attention take the mask, the sink
+            # and the gate as well (the clusters of the decode kernel, tcgen05 for long portions)
+            sm = self._sm100
+            if ctx.max_q_len == 1 and sm.decode_supported(q, cache.k, nh):
+                return sm.attention_decode(q, cache.k, cache.v, ctx.kv_lens, cache.block_table, nh, scale, window, keys,
+                                           chunk=chunk, sinks=sinks, gate=gate)
+            lens = ctx.q_lens_host
+            if ctx.max_q_len * G >= 128 and ctx.max_kv_len >= sm.TC_ATTENTION_MIN_KEYS and sm.prefill_tc_supported(q, cache.k) \
+                    and lens is not None and min(lens) * G >= 128:
+                return sm.attention_prefill_tc(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.max_q_len,
+                                               nh, scale, window, chunk=chunk, sinks=sinks, gate=gate)
+        if tc and sk.mma_supported(q.dtype, kd, vd, cache.page_size):
             tiles = 0
             for ql in (ctx.q_lens_host if not ctx.graph_safe else [1] * ctx.num_seqs):
                 tiles += (ql * G + 63) // 64
-            tiles *= cache.k.shape[1]
-            splits = max(1, min(16, self.sm_count // max(tiles, 1), keys // 128))
+            tiles *= nkv
+            # ranges of keys per row tile: up to four CTAs an SM are resident, a range is at least 128 keys
+            splits = max(1, min(16, 4 * self.sm_count // max(tiles, 1), keys // 128))
             return sk.sink_attention_mma(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, ctx.cu_q,
                                          ctx.num_seqs, ctx.max_q_len, nh, scale, window, chunk, sinks, gate, splits, keys)
         return sk.sink_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, nh, scale,

@@ -15,7 +15,7 @@ from . import ops
 from .ops import KernelError, _check, _cuda, _dt, _fn, _ptr, _stream
 
 _P, _LL = ops._P, c_longlong
-GEPI_STORE, GEPI_STORE_F32, GEPI_RELU2 = 0, 1, 2
+GEPI_STORE, GEPI_STORE_F32, GEPI_RELU2, GEPI_SILU_GATED = 0, 1, 2, 3
 
 ops.register_signatures("experts", {
     "rllm_grouped_gemm_uniform": [c_int, c_int, _P, _LL, _LL, _P, _LL, _P, _LL, _LL, c_int, c_int, c_int, c_int,
@@ -207,16 +207,19 @@ def gather_rows_bf16(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
 def grouped_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: torch.Tensor, epilogue: int,
                     scatter: bool = False, scale: bool = False, err: torch.Tensor | None = None) -> torch.Tensor:
     """The ragged product on tcgen05 (csrc/grouped_gemm_tc.cu): a [plan rows, K] bfloat16 in sorted order (no
-    gather: see gather_rows_bf16), w [E, N, K]; epilogue GEPI_RELU2 (bfloat16 out, sorted order) or
-    GEPI_STORE_F32 (float out, `scatter` to the rows' places, `scale` by their weights). The plan must have
-    tiles of 128 rows. `err`: one int32 on the device that records a bounded wait that ran out."""
+    gather: see gather_rows_bf16), w [E, N, K]; epilogue GEPI_RELU2 (bfloat16 out, sorted order),
+    GEPI_STORE_F32 (float out, `scatter` to the rows' places, `scale` by their weights) or GEPI_SILU_GATED (w's
+    rows in blocks of 16 gate rows and their 16 up rows; bfloat16 out [rows, N / 2] = silu(f g) * (f u), f the
+    row's weight with `scale`). The plan must have tiles of 128 rows. `err`: one int32 on the device that records a bounded wait that ran out."""
     E, N, K = w.shape
     _rows(a, "a", K)
-    _rows(out, "out", N)
+    _rows(out, "out", N // 2 if epilogue == GEPI_SILU_GATED else N)
     _cuda(w, "w")
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or plan.tile_rows != 128 \
-            or a.shape[0] < plan.n_rows or epilogue not in (GEPI_RELU2, GEPI_STORE_F32):
-        raise KernelError("tcgen05 grouped product: bfloat16 operands, a plan with tiles of 128 rows, relu^2 or float store")
+            or a.shape[0] < plan.n_rows or epilogue not in (GEPI_RELU2, GEPI_STORE_F32, GEPI_SILU_GATED):
+        raise KernelError("tcgen05 grouped product: bfloat16 operands, a plan with tiles of 128 rows, relu^2, float store or gated silu")
+    if epilogue == GEPI_SILU_GATED and (N % 32 or scatter):
+        raise KernelError("tcgen05 grouped product: the gated epilogue takes whole blocks of 16 + 16 rows and writes in sorted order")
     if out.dtype != (torch.float32 if epilogue == GEPI_STORE_F32 else torch.bfloat16) or out.shape[0] < plan.n_rows:
         raise KernelError(f"tcgen05 grouped product: out has dtype {out.dtype} and {out.shape[0]} rows")
     _check(_fn("experts", "rllm_grouped_gemm_tc")(

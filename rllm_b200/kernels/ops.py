@@ -41,6 +41,7 @@ _SIGS = {
         "rllm_check_meta": [_P, c_int, _P, c_int, c_int, c_int, _P, _P],
         "rllm_silu_gate": [_P, _P, c_int, c_int, c_int, _P],
         "rllm_gemm_simt": [c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+        "rllm_gemm_skinny": [c_int, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_int, _P],
         "rllm_paged_attention_simt": [c_int, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_float, c_int, _P],
         "rllm_argmax": [_P, c_int, c_int, _P, _P],
@@ -271,6 +272,22 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor
     _check(_fn("simt", "rllm_gemm_simt")(_dt(a, "a"), epilogue, a.data_ptr(), w.data_ptr(),
                                          out.data_ptr(), _ptr(bias), T, N, K, a.stride(0),
                                          out.stride(0), _stream()), "gemm_simt")
+    return out
+
+
+SKINNY_MAX = 8
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """float32 C = A W^T for a weight of at most 8 rows (a gate row, a few heads): a [T, K] (unit inner stride),
+    w contiguous [N, K] of a's dtype. One warp a row; a row's sums do not depend on the rest of the batch."""
+    _cuda(a, "a"); _cuda(w, "w")
+    if a.dim() != 2 or w.dim() != 2 or a.stride(1) != 1 or not w.is_contiguous() or a.dtype != w.dtype \
+            or w.shape[1] != a.shape[1] or w.shape[0] > SKINNY_MAX:
+        raise KernelError(f"gemm_skinny takes a [T, K] and a contiguous w [N <= {SKINNY_MAX}, K] of the same dtype")
+    out = torch.empty((a.shape[0], w.shape[0]), dtype=torch.float32, device=a.device)
+    _check(_fn("simt", "rllm_gemm_skinny")(_dt(a, "a"), a.data_ptr(), w.data_ptr(), out.data_ptr(), a.shape[0],
+                                           w.shape[0], a.shape[1], a.stride(0), out.stride(0), _stream()), "gemm_skinny")
     return out
 
 

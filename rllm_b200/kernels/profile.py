@@ -113,11 +113,11 @@ class OpProfile:
         return self._timed(cls, _nbytes(w) + T * (w.shape[0] + w.shape[1]) * 2, 2 * T * w.shape[0] * w.shape[1],
                            fn, *a, **k)
 
-    def linear(self, x, w, bias=None):
-        return self._product("linear", x, w, self._be.linear, x, w, bias=bias)
+    def linear(self, x, w, bias=None, tag=None):
+        return self._product(tag or "linear", x, w, self._be.linear, x, w, bias=bias)
 
-    def linear_f32(self, x, w):
-        return self._product("head", x, w, self._be.linear_f32, x, w)
+    def linear_f32(self, x, w, tag=None):
+        return self._product(tag or "head", x, w, self._be.linear_f32, x, w)
 
     def linear_residual(self, x, w, residual):
         cls = "o" if w.shape[0] >= w.shape[1] else "down"       # a square or widening product: the mixer's output
@@ -163,10 +163,48 @@ class OpProfile:
         return self._timed("experts_up", _nbytes(w_up) + plan.n_rows * (F + W) * x.element_size(), 2 * plan.n_rows * F * W,
                            self._be.experts_up, x, w_up, plan, act)
 
-    def experts_down(self, a, w_down, plan, T, top):
+    def experts_down(self, a, w_down, plan, T, top, scale=True):
         E, W, F = w_down.shape
         return self._timed("experts_down", _nbytes(w_down) + plan.n_rows * (F * a.element_size() + 4 * W),
-                           2 * plan.n_rows * F * W, self._be.experts_down, a, w_down, plan, T, top)
+                           2 * plan.n_rows * F * W, self._be.experts_down, a, w_down, plan, T, top, scale)
+
+    def experts_gated_up(self, x, w_gate_up, plan, block=None):
+        E, F2, W = w_gate_up.shape
+        return self._timed("experts_up", _nbytes(w_gate_up) + plan.n_rows * (F2 // 2 + W) * x.element_size(),
+                           2 * plan.n_rows * F2 * W, self._be.experts_gated_up, x, w_gate_up, plan, block)
+
+    # ---- layers that norm after the sum, attention with sink, gate and block mask
+    def stream_copy(self, h):
+        return self._timed("cast", 6 * h.numel(), 0, self._be.stream_copy, h)
+
+    def postnorm(self, h, y, *a, **k):
+        parts = y.parts if hasattr(y, "parts") else y
+        return self._timed("add+norm", _nbytes(parts, getattr(y, "extra", None)) + 10 * h.numel(), 0, self._be.postnorm, h, y, *a, **k)
+
+    def linear_act(self, x, w, act):
+        return self._product("up", x, w, self._be.linear_act, x, w, act)
+
+    def qk_norm_rope_store(self, proj, *a, **k):
+        return self._timed("qk_norm+rope", 2 * _nbytes(proj), 0, self._be.qk_norm_rope_store, proj, *a, **k)
+
+    def sink_attention(self, q, cache, ctx, nh, scale, window, chunk, sinks, gate):
+        kd, vd, nkv = cache.k.shape[3], cache.v.shape[3], cache.k.shape[1]
+        lens, qs = ctx.kv_lens_host, ctx.q_lens_host
+        if lens is None:
+            lens, qs = [ctx.max_kv_len] * ctx.num_seqs, [1] * ctx.num_seqs
+        pairs = seen_keys = 0
+        for n, ql in zip(lens, qs):
+            first = n
+            for pos in range(n - ql, n):
+                lo = max(0, pos - window + 1) if window else 0
+                if chunk:
+                    lo = max(lo, pos // chunk * chunk)
+                pairs += pos - lo + 1
+                first = min(first, lo)
+            seen_keys += n - first
+        nbytes = seen_keys * nkv * (kd + vd) * cache.k.element_size() + _nbytes(q) + q.shape[0] * nh * vd * q.element_size()
+        return self._timed("attention", nbytes, 2 * nh * (kd + vd) * pairs, self._be.sink_attention, q, cache, ctx, nh, scale,
+                           window, chunk, sinks, gate)
 
     def latent_prepare(self, proj, *a, **k):
         return self._timed("latent_prepare", 2 * _nbytes(proj), 0, self._be.latent_prepare, proj, *a, **k)

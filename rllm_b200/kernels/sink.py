@@ -25,7 +25,7 @@ ops.register_signatures("sink", {
                                 c_int, c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, _P, _P, _P],
     "rllm_postnorm": [_P, _P, c_int, _P, _P, c_int, c_float, _P, c_int, c_int, c_float, _P, c_int, _P],
     "rllm_cast_rows": [_P, _P, _LL, _P],
-    "rllm_gated_act": [_P, c_int, _LL, _P, c_int, c_int, c_int, _P, _P],
+    "rllm_gated_act": [_P, c_int, _LL, _P, c_int, c_int, c_int, c_int, _P, _P],
     "rllm_relu2": [_P, c_int, _LL, _P],
 })
 
@@ -195,9 +195,11 @@ def cast_rows(h: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def gated_act(gu: torch.Tensor, out_dtype: torch.dtype, row_scale: torch.Tensor | None = None) -> torch.Tensor:
-    """out[r, i] = silu(f_r * gu[r, i]) * (f_r * gu[r, F + i]) for gu [R, 2F] (float32 or bfloat16), f_r =
-    row_scale[r] (float [R]) or 1."""
+def gated_act(gu: torch.Tensor, out_dtype: torch.dtype, row_scale: torch.Tensor | None = None,
+              block: int | None = None) -> torch.Tensor:
+    """out[r, i] = silu(f_r * g) * (f_r * u) for gu [R, 2F] (float32 or bfloat16), f_r = row_scale[r] (float [R])
+    or 1. The columns of gu: all F gate columns, then all up columns (`block` None), or blocks of `block` gate
+    columns each followed by their up columns."""
     _cuda(gu, "gu")
     if gu.dim() != 2 or gu.stride(1) != 1 or gu.shape[1] % 2:
         raise KernelError("gated_act takes [R, 2F] with unit inner stride")
@@ -206,9 +208,12 @@ def gated_act(gu: torch.Tensor, out_dtype: torch.dtype, row_scale: torch.Tensor 
         _f32(row_scale, "row_scale")
         if row_scale.numel() < R:
             raise KernelError("gated_act: one scale per row")
+    block = F if block is None else int(block)
+    if block <= 0 or F % block:
+        raise KernelError(f"gated_act: blocks of {block} do not divide {F} columns")
     out = torch.empty((R, F), dtype=out_dtype, device=gu.device)
     _check(_fn("sink", "rllm_gated_act")(gu.data_ptr(), _dt(gu, "gu"), gu.stride(0), out.data_ptr(), _dt(out, "out"), R, F,
-                                         _ptr(row_scale), _stream()), "gated_act")
+                                         block, _ptr(row_scale), _stream()), "gated_act")
     return out
 
 

@@ -29,9 +29,9 @@ ops.register_signatures("sm100", {
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
     "rllm_attention_prefill_tc": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_int, c_float, c_int, _P, c_int, _P],
+                                  c_int, c_int, c_float, c_int, c_int, _P, _P, c_int, _P, c_int, _P],
     "rllm_attention_decode": [_P, c_int, _P, _P, c_longlong, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_float, c_int, c_int, _P, _P],
+                              c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, _P, _P],
 })
 
 
@@ -322,9 +322,24 @@ def prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor) -> bool:
             and kcache.is_contiguous() and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and kcache.data_ptr() % 16 == 0)
 
 
-def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_len, nh, scale, window, out=None):
+def _extras(chunk, sinks, gate, nh, rows):
+    """(chunk, sinks pointer, gate pointer, gate row stride) of an attention call, checked."""
+    if sinks is not None and (sinks.dtype != torch.float32 or not sinks.is_cuda or not sinks.is_contiguous()
+                              or sinks.numel() != nh):
+        raise ops.KernelError(f"attention: sinks must be a contiguous float32 vector of {nh} on the device")
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate.dim() != 2 or gate.stride(1) != 1
+                             or gate.shape[0] < rows or gate.shape[1] < nh):
+        raise ops.KernelError(f"attention: the gate must be float32 [>= {rows}, >= {nh}] with unit inner stride")
+    return (int(chunk or 0), None if sinks is None else sinks.data_ptr(), None if gate is None else gate.data_ptr(),
+            0 if gate is None else gate.stride(0))
+
+
+def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_len, nh, scale, window, out=None,
+                         chunk=None, sinks=None, gate=None):
     """Prefill attention on the tcgen05 tensor cores (bf16, head size 64 or 128): tiles of 128 rows x
-    128 (64) keys, both products with their accumulators in TMEM."""
+    128 (64) keys, both products with their accumulators in TMEM. `chunk`: a query sees only the keys of its
+    own block of that many positions; `sinks` float [nh]: exp(sink) joins a row's denominator; `gate` float
+    logits [T, >= nh]: head h's output times sigmoid(gate[t, h])."""
     if not prefill_tc_supported(q, kcache):
         raise ops.KernelError("attention_prefill_tc: bfloat16, head size 64 or 128, rows 16-byte aligned")
     st = init(q.device)
@@ -334,8 +349,8 @@ def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_le
     rc = ops._fn("sm100", "rllm_attention_prefill_tc")(
         q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
         cu_q.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), kv_lens.numel(),
-        max_q_len, kcache.shape[0], nh, nkv, hd, page_size, float(scale), int(window or 0), st.err.data_ptr(),
-        st.sm_count, ops._stream())
+        max_q_len, kcache.shape[0], nh, nkv, hd, page_size, float(scale), int(window or 0),
+        *_extras(chunk, sinks, gate, nh, q.shape[0]), st.err.data_ptr(), st.sm_count, ops._stream())
     ops._check(rc, "attention_prefill_tc")
     return out
 
@@ -371,7 +386,7 @@ def decode_splits(num_seqs: int, nkv: int, max_kv_len: int, sm_count: int) -> in
 
 
 def attention_decode(q, kcache, vcache, kv_lens, block_table, nh, scale, window, max_kv_len, splits=None,
-                     out=None):
+                     out=None, chunk=None, sinks=None, gate=None):
     """Attention for a step in which every sequence brings one token: the ranges of a sequence's
     keys are merged inside a thread-block cluster (bf16, head size 64 or 128, any page size)."""
     st = init(q.device)
@@ -390,7 +405,8 @@ def attention_decode(q, kcache, vcache, kv_lens, block_table, nh, scale, window,
     rc = ops._fn("sm100", "rllm_attention_decode")(
         q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), num_pages, out.data_ptr(),
         out.stride(0), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), S, nh, nkv, hd,
-        page_size, float(scale), int(window or 0), int(splits), st.err.data_ptr(), ops._stream())
+        page_size, float(scale), int(window or 0), *_extras(chunk, sinks, gate, nh, S), int(splits), st.err.data_ptr(),
+        ops._stream())
     ops._check(rc, "attention_decode")
     return out
 

@@ -131,14 +131,14 @@ class SinkGQAttention(Part):
         be = ctx.backend
         x = x.tensor() if hasattr(x, "tensor") else x
         H, G, D, V = self.heads, self.kv_heads, self.head_dim, self.v_dim
-        proj = be.linear(x, self.w_qkv)                                  # [T, q | k | v]
-        gate = be.linear_f32(x, self.w_g) if self.gate else None         # float logits [T, H]
+        proj = be.linear(x, self.w_qkv, tag="qkv")                                  # [T, q | k | v]
+        gate = be.linear_f32(x, self.w_g, tag="gate") if self.gate else None         # float logits [T, H]
         pos = self.position
         be.qk_norm_rope_store(proj, 0, H * D, (H + G) * D, H, G, D, V, 0 if pos is None else pos.rot_dim,
                               self._qn, self._kn, self.eps, None if pos is None else pos.table(ctx), cache)
         att = be.sink_attention(proj[:, : H * D], cache, ctx, H, self.scale, self.window, self.chunk, self._sinks, gate)
         if residual is None:
-            return be.linear_f32(att, self.w_o)
+            return be.linear_f32(att, self.w_o, tag="o")
         be.linear_residual(att, self.w_o, residual)
         return None
 

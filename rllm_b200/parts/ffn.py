@@ -28,7 +28,7 @@ class SwiGLU(Part):
         be = ctx.backend
         act = be.linear_swiglu(x, self.w_gate_up)
         if residual is None:
-            return be.linear_f32(act, self.w_down)
+            return be.linear_f32(act, self.w_down, tag="down")
         be.linear_residual(act, self.w_down, residual)
 
 
@@ -52,7 +52,7 @@ class ActFFN(Part):
         be = ctx.backend
         a = be.linear_act(x, self.w_up, self.act)
         if residual is None:
-            return be.linear_f32(a, self.w_down)
+            return be.linear_f32(a, self.w_down, tag="down")
         be.linear_residual(a, self.w_down, residual)
 
 

@@ -85,8 +85,16 @@ class GatedRoutedExperts(Part):
         return ps
 
     def finalize(self, device, dtype):
-        self._gate_up = self.w_gate_up.view(self.experts, 2 * self.ff, self.hidden)
-        self._down = self.w_down.view(self.experts, self.hidden, self.ff)
+        E, F, W = self.experts, self.ff, self.hidden
+        self._block = 16 if F % 16 == 0 else None
+        if self._block and getattr(self, "_arranged", None) is not self.w_gate_up:
+            # as bound: per expert its gate rows, then its up rows. Where the inner size allows it the rows are
+            # kept in blocks of 16 gate rows each followed by their 16 up rows, so that a tile of the product
+            # holds both halves of its outputs and the kernel can activate in its epilogue. One copy is kept.
+            gu = self.w_gate_up.view(E, 2, F // 16, 16, W).permute(0, 2, 1, 3, 4).contiguous()
+            self.w_gate_up = self._arranged = gu.view(E * 2 * F, W)
+        self._gate_up = self.w_gate_up.view(E, 2 * F, W)
+        self._down = self.w_down.view(E, W, F)
 
     def forward(self, x, ctx, residual=None):
         if residual is not None:
@@ -94,14 +102,14 @@ class GatedRoutedExperts(Part):
         be = ctx.backend
         x = x.tensor() if hasattr(x, "tensor") else x
         T = x.shape[0]
-        _, _, plan = be.route(be.linear_f32(x, self.w_router), self.top, renorm=self.renorm, score=self.score,
+        _, _, plan = be.route(be.linear_f32(x, self.w_router, tag="router"), self.top, renorm=self.renorm, score=self.score,
                               tile_rows=be.expert_tile_rows(x, self._gate_up, self._down, T * self.top))
-        act = be.experts_gated_up(x, self._gate_up, plan)             # silu(w g) * (w u), sorted rows
+        act = be.experts_gated_up(x, self._gate_up, plan, self._block)        # silu(w g) * (w u), sorted rows
         parts = be.experts_down(act, self._down, plan, T, self.top, scale=False)
         if self.shared is None:
             return Summands(parts)
         return Summands(parts, self.shared.forward(x, ctx, None),
-                        be.linear_f32(x, self.w_sg) if self.shared_gate else None)
+                        be.linear_f32(x, self.w_sg, tag="gate") if self.shared_gate else None)
 
 
 register_part("ffn", "moe", RoutedExperts)

@@ -207,6 +207,85 @@ def test_decoding_deals_the_keys_out_to_several_ctas(chunk, window):
         assert rel(got, want) < 2e-2, splits
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("chunk,window", [(None, None), (200, None), (1024, 300), (64, None)])
+def test_the_kernels_of_plain_attention_take_mask_sink_and_gate(hd, chunk, window):
+    """Equal key and value sizes of 64 or 128: the cluster kernel for single tokens and the tcgen05 kernel for long
+    portions, with a block mask, a sink and a gate, against the float kernel on the same cache. Keys just inside
+    and just outside the last query's block are made to win."""
+    from rllm_b200.kernels import sink, sm100
+    g = torch.Generator().manual_seed(hd)
+    nh, nkv, page, n_pages = 8, 2, 16, 100
+    lens, qlens = [1500, 700, 1024], [600, 700, 130]
+    S = len(lens)
+    kc = (torch.randn(n_pages * S, nkv, page, hd, generator=g) * 0.5).bfloat16().to(DEV)
+    vc = torch.randn(n_pages * S, nkv, page, hd, generator=g).bfloat16().to(DEV)
+    bt = torch.arange(n_pages * S, dtype=torch.int32).view(S, n_pages).flip(0).contiguous().to(DEV)
+    sinks = (torch.randn(nh, generator=g) * 3).to(DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    # single tokens
+    q = torch.randn(S, nh * hd, generator=g).bfloat16().to(DEV)
+    start = 1499 // chunk * chunk if chunk else 0
+    for far in (max(start - 1, 0), start, 1499 - 250):
+        kc[bt[0, far // page].item(), :, far % page] = q[0].view(nh, hd)[::4] * 2
+    pos = kv - 1
+    seq = torch.arange(S, dtype=torch.int32, device=DEV)
+    gate = torch.randn(S, nh, generator=g).to(DEV)
+    want = sink.sink_attention_simt(q, kc, vc, seq, pos, bt, nh, 0.11, window, chunk, sinks, gate)
+    for splits in (1, 4, 8):
+        got = sm100.attention_decode(q, kc, vc, kv, bt, nh, 0.11, window, 1500, splits=splits, chunk=chunk, sinks=sinks, gate=gate)
+        assert rel(got, want) < 2e-2, splits
+    # long portions
+    T = sum(qlens)
+    q = torch.randn(T, nh * hd, generator=g).bfloat16().to(DEV)
+    cu = torch.tensor([0, 600, 1300, 1430], dtype=torch.int32, device=DEV)
+    pos = torch.cat([torch.arange(n - ql, n) for n, ql in zip(lens, qlens)]).int().to(DEV)
+    seq = torch.cat([torch.full((ql,), i) for i, ql in enumerate(qlens)]).int().to(DEV)
+    gate = torch.randn(T, nh, generator=g).to(DEV)
+    want = sink.sink_attention_simt(q, kc, vc, seq, pos, bt, nh, 0.11, window, chunk, sinks, gate)
+    got = sm100.attention_prefill_tc(q, kc, vc, cu, kv, bt, max(qlens), nh, 0.11, window, chunk=chunk, sinks=sinks, gate=gate)
+    assert rel(got, want) < 2e-2
+    got = sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, S, max(qlens), nh, 0.11, window, chunk, sinks, gate)
+    assert rel(got, want) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("N,K", [(1, 40), (6, 256), (8, 1000), (3, 7)])
+def test_product_with_a_few_weight_rows(dtype, N, K):
+    from rllm_b200.kernels import ops
+    x, w = rnd(21, K, seed=1).to(DT[dtype]), rnd(N, K, seed=2).to(DT[dtype])
+    got = ops.gemm_skinny(x.to(DEV), w.to(DEV))
+    assert got.dtype == torch.float32 and rel(got, x.double() @ w.double().T) < 3e-6
+
+
+def test_long_row_lists_of_gated_experts_run_on_tcgen05():
+    """1,400 (token, expert) rows: the grouped products take the tcgen05 kernel, the gate/up product activates in
+    its epilogue on weights kept in blocks of 16 + 16 rows. Against the plain implementation."""
+    from rllm_b200.parts import GatedRoutedExperts
+    W, F, E, top, T = 64, 64, 5, 2, 700
+    w = {"router": rnd(E, W, seed=1, scale=0.5)}
+    for e in range(E):
+        w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"] = rnd(F, W, seed=10 + e, scale=0.3), rnd(F, W, seed=40 + e, scale=0.3), rnd(W, F, seed=70 + e, scale=0.3)
+    ffn = GatedRoutedExperts(W, F, E, top, score="sigmoid")
+    ffn.set_prefix("x.mlp.")
+    bind_tree(ffn, {"x.mlp." + k: v for k, v in w.items()}, "bfloat16")
+    x = rnd(T, W, seed=2).bfloat16()
+    want = P.moe_ffn(x.double(), as_stored(w, "bfloat16"), {"router": {"experts": E, "top": top}})
+
+    class Ctx:
+        backend = Harness("bfloat16", []).backend
+    seen = []
+    be = Ctx.backend
+    orig = be._mix.grouped_gemm_tc
+    be._mix.grouped_gemm_tc = lambda *a, **k: (seen.append(a[4]), orig(*a, **k))[1]
+    try:
+        out = ffn.forward(x.to(DEV), Ctx)
+    finally:
+        be._mix.grouped_gemm_tc = orig
+    assert seen == [be._mix.GEPI_SILU_GATED, be._mix.GEPI_STORE_F32]
+    assert rel(out.parts.sum(1), want) < 2e-2
+
+
 # ------------------------------------------------------------------ feed-forwards in a post-norm block
 
 @pytest.mark.parametrize("dtype", list(DT))
