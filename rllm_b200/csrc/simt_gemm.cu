@@ -108,35 +108,72 @@ int launch(int epi, const void* A, const void* W, void* C, const void* bias, int
   return rc;
 }
 
-// Few outputs a row (a gate row, a handful of heads or experts): one warp a row of A, the lanes stride over K
+// Few outputs a row (a gate row, a handful of heads or experts): a CTA a row of A, the threads stride over K
 // and keep one sum per output; a row's sums are added in one fixed order whatever else the batch holds.
 constexpr int SKINNY_MAX = 8;
 
-template <typename TI>
-__global__ void __launch_bounds__(128)
+template <typename TI> struct Piece {};
+template <> struct Piece<float> { static constexpr int N = 4; typedef float4 V;
+  static __device__ __forceinline__ void get(const float4& v, float* f) { f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; } };
+template <> struct Piece<bf16> { static constexpr int N = 8; typedef uint4 V;
+  static __device__ __forceinline__ void get(const uint4& v, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  } };
+
+// A CTA of `blockDim.x / 32` warps a row; VEC: rows of A and W start on 16 bytes and K is a whole number of 16-byte
+// pieces, which the threads then stride over; else element by element. Warp sums, then the warps in order.
+template <typename TI, bool VEC>
+__global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const TI* __restrict__ A, const TI* __restrict__ W, float* __restrict__ C, int T, int N, int K,
                    long long lda, int ldc) {
   pdl_launch();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long t = (long long)blockIdx.x * 4 + warp;
-  if (t >= T) return;
+  __shared__ float part[8][SKINNY_MAX];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const long long t = blockIdx.x;
   const TI* a = A + t * lda;
   float acc[SKINNY_MAX];
 #pragma unroll
   for (int n = 0; n < SKINNY_MAX; ++n) acc[n] = 0.f;
-  for (int k = lane; k < K; k += 32) {
-    const float x = to_f32(a[k]);
+  if (VEC) {
+    typedef typename Piece<TI>::V V;
+    constexpr int PN = Piece<TI>::N;
+    const int pieces = K / PN;
+    for (int c = threadIdx.x; c < pieces; c += blockDim.x) {
+      float x[PN];
+      Piece<TI>::get(reinterpret_cast<const V*>(a)[c], x);
 #pragma unroll
-    for (int n = 0; n < SKINNY_MAX; ++n)
-      if (n < N) acc[n] = fmaf(x, to_f32(W[(size_t)n * K + k]), acc[n]);
+      for (int n = 0; n < SKINNY_MAX; ++n) {
+        if (n < N) {
+          float wv[PN];
+          Piece<TI>::get(reinterpret_cast<const V*>(W + (size_t)n * K)[c], wv);
+#pragma unroll
+          for (int i = 0; i < PN; ++i) acc[n] = fmaf(x[i], wv[i], acc[n]);
+        }
+      }
+    }
+  } else {
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      const float x = to_f32(a[k]);
+#pragma unroll
+      for (int n = 0; n < SKINNY_MAX; ++n)
+        if (n < N) acc[n] = fmaf(x, to_f32(W[(size_t)n * K + k]), acc[n]);
+    }
   }
 #pragma unroll
   for (int n = 0; n < SKINNY_MAX; ++n) {
     if (n < N) {
       const float v = warp_sum(acc[n]);
-      if (lane == 0) C[t * ldc + n] = v;
+      if (lane == 0) part[warp][n] = v;
     }
+  }
+  __syncthreads();
+  if (threadIdx.x < N) {
+    float v = 0.f;
+    for (int w2 = 0; w2 < nw; ++w2) v += part[w2][threadIdx.x];
+    C[t * ldc + threadIdx.x] = v;
   }
 }
 
@@ -147,15 +184,20 @@ RLLM_API int rllm_gemm_skinny(int dt, const void* A, const void* W, float* C, in
                               int ldc, void* stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || N > SKINNY_MAX) return ERR_BAD_SIZE;
-  const long long blocks = ((long long)T + 3) / 4;
-  if (blocks > 2147483647LL) return ERR_TOO_LARGE;
+  if (T > 2147483647LL) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
+  const int esz = dt == DT_F32 ? 4 : 2, pn = 16 / esz;
+  const bool vec = K % pn == 0 && lda % pn == 0 && !((uintptr_t)A & 15) && !((uintptr_t)W & 15);
+  // warps a row: as many as the row has 16-byte pieces for, up to eight (the count depends on K alone)
+  int warps = vec ? (K / pn + 31) / 32 : (K + 255) / 256;
+  warps = warps < 1 ? 1 : (warps > 8 ? 8 : warps);
+  const dim3 grid((unsigned)T), block(32 * warps);
   if (dt == DT_F32)
-    return launch_ex(gemm_skinny_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (const float*)A,
-                     (const float*)W, C, T, N, K, lda, ldc);
+    return vec ? launch_ex(gemm_skinny_kernel<float, true>, grid, block, 0, s, 1, (const float*)A, (const float*)W, C, T, N, K, lda, ldc)
+               : launch_ex(gemm_skinny_kernel<float, false>, grid, block, 0, s, 1, (const float*)A, (const float*)W, C, T, N, K, lda, ldc);
   if (dt == DT_BF16)
-    return launch_ex(gemm_skinny_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (const bf16*)A,
-                     (const bf16*)W, C, T, N, K, lda, ldc);
+    return vec ? launch_ex(gemm_skinny_kernel<bf16, true>, grid, block, 0, s, 1, (const bf16*)A, (const bf16*)W, C, T, N, K, lda, ldc)
+               : launch_ex(gemm_skinny_kernel<bf16, false>, grid, block, 0, s, 1, (const bf16*)A, (const bf16*)W, C, T, N, K, lda, ldc);
   return ERR_BAD_DTYPE;
 }
 

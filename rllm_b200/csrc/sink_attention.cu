@@ -69,6 +69,89 @@ qk_norm_rope_store_kernel(T* __restrict__ proj, long long ld, int q_off, int k_o
   }
 }
 
+// The same for bfloat16 rows in 16-byte pieces (head sizes multiples of 8, rotated width a multiple of 16): LPH lanes
+// a head, each with one piece of 8 numbers and, inside the rotated part, a second look at the piece it pairs
+// with; the sum of squares crosses the head's lanes by shuffles. Nothing is staged: all loads of a warp are
+// issued before its first store (queries are rewritten in place).
+template <int LPH>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_store_vec_kernel(bf16* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, int n_tokens, int nh,
+                              int nkv, int kd, int vd, int rot, const float* __restrict__ wq, const float* __restrict__ wk,
+                              float eps, const float* __restrict__ table, const int* __restrict__ slots,
+                              bf16* __restrict__ kcache, bf16* __restrict__ vcache, int page_size) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int HPW = 32 / LPH;                      // heads a warp
+  const int lane = threadIdx.x & 31;
+  const int per = nh + 2 * nkv;
+  const long long item = ((long long)blockIdx.x * 4 + (threadIdx.x >> 5)) * HPW + lane / LPH;
+  const int c = lane % LPH;
+  const bool live = item < (long long)n_tokens * per;
+  const int t = live ? (int)(item / per) : 0, u = live ? (int)(item % per) : 0;
+  bf16* row = proj + (long long)t * ld;
+  const int slot = (live && slots) ? slots[t] : -1;
+  const bool is_q = u < nh, is_v = u >= nh + nkv;
+  const int size = is_v ? vd : kd;
+  const bool mine = live && c * 8 < size && (is_q || slot >= 0);
+  bf16* src = is_q ? row + q_off + u * kd : (is_v ? row + v_off + (u - nh - nkv) * vd : row + k_off + (u - nh) * kd);
+  const int half = rot / 2;
+  const bool turns = mine && !is_v && table && c * 8 < rot;
+  const int cp = c * 8 < half ? c + half / 8 : c - half / 8;             // the piece this one pairs with
+  uint4 own = make_uint4(0, 0, 0, 0), other = make_uint4(0, 0, 0, 0);
+  if (mine) own = *reinterpret_cast<const uint4*>(src + c * 8);
+  if (turns) other = *reinterpret_cast<const uint4*>(src + cp * 8);
+  float x[8], y[8];
+  {
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&own);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&other);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(a[i]), g = __bfloat1622float2(b[i]);
+      x[2 * i] = f.x; x[2 * i + 1] = f.y; y[2 * i] = g.x; y[2 * i + 1] = g.y;
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float* w = is_q ? wq : wk;
+  if (mine && !is_v && w) {
+    const float r = 1.f / sqrtf(ss / (float)kd + eps);
+    const float4 w0 = reinterpret_cast<const float4*>(w + c * 8)[0], w1 = reinterpret_cast<const float4*>(w + c * 8)[1];
+    x[0] *= r * w0.x; x[1] *= r * w0.y; x[2] *= r * w0.z; x[3] *= r * w0.w;
+    x[4] *= r * w1.x; x[5] *= r * w1.y; x[6] *= r * w1.z; x[7] *= r * w1.w;
+    if (turns) {
+      const float4 p0 = reinterpret_cast<const float4*>(w + cp * 8)[0], p1 = reinterpret_cast<const float4*>(w + cp * 8)[1];
+      y[0] *= r * p0.x; y[1] *= r * p0.y; y[2] *= r * p0.z; y[3] *= r * p0.w;
+      y[4] *= r * p1.x; y[5] *= r * p1.y; y[6] *= r * p1.z; y[7] *= r * p1.w;
+    }
+  }
+  if (turns) {
+    const int f0 = (c * 8) % half;
+    const float4* cs = reinterpret_cast<const float4*>(table + ((long long)t * half + f0) * 2);
+    const float sg = c * 8 < half ? -1.f : 1.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = cs[i];                           // (cos, sin) of two frequencies
+      x[2 * i] = x[2 * i] * v.x + sg * y[2 * i] * v.y;
+      x[2 * i + 1] = x[2 * i + 1] * v.z + sg * y[2 * i + 1] * v.w;
+    }
+  }
+  __syncwarp();                                         // every load of the warp is done: queries may be rewritten
+  if (!mine) return;
+  bf16* dst = src;
+  if (!is_q) {
+    const int g = is_v ? u - nh - nkv : u - nh;
+    dst = (is_v ? vcache : kcache) + (((long long)(slot / page_size) * nkv + g) * page_size + slot % page_size) * size;
+  }
+  uint4 o;
+  __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+  *reinterpret_cast<uint4*>(dst + c * 8) = o;
+}
+
 constexpr int WARPS = 4;
 
 template <typename T> struct Vec16 {};
@@ -199,6 +282,30 @@ RLLM_API int rllm_qk_norm_rope_store(int dt, void* proj, long long ld, int q_off
     return launch_ex(qk_norm_rope_store_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (float*)proj, ld, q_off,
                      k_off, v_off, n_tokens, nh, nkv, kd, vd, rot, wq, wk, eps, table, slots, (float*)kcache,
                      (float*)vcache, page_size);
+  const bool vec = dt == DT_BF16 && kd % 8 == 0 && vd % 8 == 0 && rot % 16 == 0 && ld % 8 == 0 && q_off % 8 == 0 &&
+                   k_off % 8 == 0 && v_off % 8 == 0 && !((uintptr_t)proj & 15) && !((uintptr_t)kcache & 15) &&
+                   !((uintptr_t)vcache & 15) && !((uintptr_t)wq & 15) && !((uintptr_t)wk & 15) && !((uintptr_t)table & 15) &&
+                   (slots != nullptr) == (kcache != nullptr && vcache != nullptr);
+  if (vec) {
+    const int pieces = (kd > vd ? kd : vd) / 8;
+    int lph = 1;
+    while (lph < pieces) lph *= 2;
+    const long long items = (long long)n_tokens * (nh + 2 * nkv);
+    const long long vblocks = (items + 4 * (32 / lph) - 1) / (4 * (32 / lph));
+    if (vblocks > 2147483647LL) return ERR_TOO_LARGE;
+#define GO(L) return launch_ex(qk_norm_rope_store_vec_kernel<L>, dim3((unsigned)vblocks), dim3(128), 0, s, 1, (bf16*)proj, ld, \
+                               q_off, k_off, v_off, n_tokens, nh, nkv, kd, vd, rot, wq, wk, eps, table, slots, (bf16*)kcache,  \
+                               (bf16*)vcache, page_size)
+    switch (lph) {
+      case 1: GO(1);
+      case 2: GO(2);
+      case 4: GO(4);
+      case 8: GO(8);
+      case 16: GO(16);
+      default: GO(32);
+    }
+#undef GO
+  }
   if (dt == DT_BF16)
     return launch_ex(qk_norm_rope_store_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (bf16*)proj, ld, q_off,
                      k_off, v_off, n_tokens, nh, nkv, kd, vd, rot, wq, wk, eps, table, slots, (bf16*)kcache,

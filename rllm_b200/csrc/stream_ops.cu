@@ -44,6 +44,83 @@ __global__ void postnorm_kernel(float* __restrict__ h, const float* __restrict__
   }
 }
 
+// The same for rows of 4 * VPT * blockDim numbers at most: every thread keeps VPT float4 of the row in registers,
+// all of a row's loads are in flight together (a step of single tokens is a handful of rows: latency is all).
+template <typename TO, int VPT>
+__global__ void __launch_bounds__(1024) postnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ y, int parts,
+                                                           const float* __restrict__ y2, const float* __restrict__ zg,
+                                                           int zg_ld, float alpha, const float* __restrict__ w, int H,
+                                                           float eps, TO* __restrict__ copy) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float red[32];
+  const size_t t = blockIdx.x;
+  const int n4 = H / 4;
+  float4* hr = reinterpret_cast<float4*>(h + t * H);
+  const float4* yr = y ? reinterpret_cast<const float4*>(y + t * parts * H) : nullptr;
+  const float4* y2r = y2 ? reinterpret_cast<const float4*>(y2 + t * H) : nullptr;
+  float4 v[VPT], e[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    v[k] = i < n4 ? hr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    e[k] = (y2r && i < n4) ? y2r[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const float g2 = (y2 && zg) ? 1.f / (1.f + expf(-zg[t * zg_ld])) : 1.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) { v[k].x *= alpha; v[k].y *= alpha; v[k].z *= alpha; v[k].w *= alpha; }
+  if (yr) {
+    for (int p = 0; p < parts; ++p) {
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4) { const float4 a = yr[(size_t)p * n4 + i]; v[k].x += a.x; v[k].y += a.y; v[k].z += a.z; v[k].w += a.w; }
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    if (y2r) { v[k].x = fmaf(g2, e[k].x, v[k].x); v[k].y = fmaf(g2, e[k].y, v[k].y); v[k].z = fmaf(g2, e[k].z, v[k].z); v[k].w = fmaf(g2, e[k].w, v[k].w); }
+    ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss); ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < n4) {
+      const float4 ww = reinterpret_cast<const float4*>(w)[i];
+      const float4 o = make_float4(v[k].x * r * ww.x, v[k].y * r * ww.y, v[k].z * r * ww.z, v[k].w * r * ww.w);
+      hr[i] = o;
+      if (copy) {
+        TO* c = copy + t * H + 4 * (size_t)i;
+        c[0] = from_f32<TO>(o.x); c[1] = from_f32<TO>(o.y); c[2] = from_f32<TO>(o.z); c[3] = from_f32<TO>(o.w);
+      }
+    }
+  }
+}
+
+template <typename TO>
+int launch_postnorm(float* h, const float* y, int parts, const float* y2, const float* zg, int zg_ld, float alpha,
+                    const float* w, int T, int H, float eps, TO* copy, cudaStream_t s) {
+  const bool vec = H % 4 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)y & 15) && !((uintptr_t)y2 & 15) && !((uintptr_t)w & 15);
+  if (vec && H <= 4 * 1024 * 4) {
+    const int n4 = H / 4;
+    if (n4 <= 1024) {
+      const int threads = (n4 + 31) / 32 * 32;
+      return launch_ex(postnorm_vec_kernel<TO, 1>, dim3(T), dim3(threads), 0, s, 1, h, y, parts, y2, zg, zg_ld, alpha, w, H, eps, copy);
+    }
+    const int threads = ((n4 + 3) / 4 + 31) / 32 * 32;
+    return launch_ex(postnorm_vec_kernel<TO, 4>, dim3(T), dim3(threads), 0, s, 1, h, y, parts, y2, zg, zg_ld, alpha, w, H, eps, copy);
+  }
+  static bool done[64] = {};
+  const int smem = H * (int)sizeof(float);
+  if (smem > 48 * 1024) { const int rc = allow_dynamic_smem(postnorm_kernel<TO>, smem, done); if (rc) return rc; }
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  return launch_ex(postnorm_kernel<TO>, dim3(T), dim3(threads), (size_t)smem, s, 1, h, y, parts, y2, zg, zg_ld, alpha, w, H, eps, copy);
+}
+
 __global__ void cast_rows_kernel(const float* __restrict__ x, bf16* __restrict__ out, long long n) {
   pdl_launch();
   pdl_wait();
@@ -76,6 +153,22 @@ __global__ void relu2_kernel(T* __restrict__ x, long long n) {
   }
 }
 
+__global__ void relu2_bf16x8_kernel(uint4* __restrict__ x, long long n8) {
+  pdl_launch();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    uint4 v = x[i];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __bfloat1622float2(h[k]);
+      f.x = fmaxf(f.x, 0.f); f.y = fmaxf(f.y, 0.f);
+      h[k] = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+    }
+    x[i] = v;
+  }
+}
+
 inline int blocks_for(long long n) { return (int)((n + 255) / 256 < 2368 ? (n + 255) / 256 : 2368); }
 
 }  // namespace
@@ -86,20 +179,11 @@ RLLM_API int rllm_postnorm(float* h, const float* y, int parts, const float* y2,
                            const float* w, int T, int H, float eps, void* copy, int copy_dt, void* stream) {
   if (T <= 0) return 0;
   if (H <= 0 || parts < 0 || (size_t)H * sizeof(float) > 200 * 1024) return ERR_BAD_SIZE;
-  const int smem = H * (int)sizeof(float);
-  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
-  if (copy && copy_dt == DT_BF16) {
-    static bool done[64] = {};
-    if (smem > 48 * 1024) { const int rc = allow_dynamic_smem(postnorm_kernel<bf16>, smem, done); if (rc) return rc; }
-    return launch_ex(postnorm_kernel<bf16>, dim3(T), dim3(threads), (size_t)smem, s, 1, h, y, parts, y2, zg, zg_ld, alpha, w,
-                     H, eps, (bf16*)copy);
-  }
+  if (copy && copy_dt == DT_BF16)
+    return launch_postnorm<bf16>(h, y, parts, y2, zg, zg_ld, alpha, w, T, H, eps, (bf16*)copy, s);
   if (copy && copy_dt != DT_F32) return ERR_BAD_DTYPE;
-  static bool done[64] = {};
-  if (smem > 48 * 1024) { const int rc = allow_dynamic_smem(postnorm_kernel<float>, smem, done); if (rc) return rc; }
-  return launch_ex(postnorm_kernel<float>, dim3(T), dim3(threads), (size_t)smem, s, 1, h, y, parts, y2, zg, zg_ld, alpha, w,
-                   H, eps, (float*)copy);
+  return launch_postnorm<float>(h, y, parts, y2, zg, zg_ld, alpha, w, T, H, eps, (float*)copy, s);
 }
 
 RLLM_API int rllm_cast_rows(const float* x, void* out, long long n, void* stream) {
@@ -128,6 +212,8 @@ RLLM_API int rllm_relu2(void* x, int dt, long long n, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (dt == DT_F32) return launch_ex(relu2_kernel<float>, dim3(blocks_for(n)), dim3(256), 0, s, 1, (float*)x, n);
+  if (dt == DT_BF16 && n % 8 == 0 && !((uintptr_t)x & 15))
+    return launch_ex(relu2_bf16x8_kernel, dim3(blocks_for(n / 8)), dim3(256), 0, s, 1, (uint4*)x, n / 8);
   if (dt == DT_BF16) return launch_ex(relu2_kernel<bf16>, dim3(blocks_for(n)), dim3(256), 0, s, 1, (bf16*)x, n);
   return ERR_BAD_DTYPE;
 }
