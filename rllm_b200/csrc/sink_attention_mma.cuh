@@ -37,6 +37,16 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ float fast_exp2(float x) {          // exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -52,6 +62,7 @@ struct Args {
   int window, chunk;
   const float* sinks; const float* gate; int gate_ld;
   int splits; float* pacc; float* pml;
+  int page_shift;              // log2(page_size), or -1 when it is no power of two
 };
 
 __device__ __forceinline__ int first_key(int pos, int window, int chunk) {
@@ -98,20 +109,22 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   __syncthreads();
 
   const int kchunks = p.kd / 8, vchunks = p.vd / 8;
+  // two threads a key row, each with every other 16-byte piece of the key and of the value: one page look-up a
+  // thread and tile
+  const int lk = tid >> 1, lh = tid & 1;
   auto load_tile = [&](int tile, int stage) {
-    const int key0 = tile * KEYS;
-    bf16* kd_ = Ks + stage * KEYS * LD;
-    bf16* vd_ = Vs + stage * KEYS * LD;
-    for (int c = tid; c < KEYS * (kchunks + vchunks); c += THREADS) {
-      const int key = c / (kchunks + vchunks), part = c % (kchunks + vchunks);
-      const int j = key0 + key;
-      bool ok = j >= key_lo && j <= pos_hi;
-      const int page = ok ? bt[j / p.page_size] : -1;
-      ok = ok && page >= 0;
-      const long long slot = ok ? ((long long)page * p.nkv + g) * p.page_size + j % p.page_size : 0;
-      if (part < kchunks) cp_async16(kd_ + key * LD + part * 8, p.kcache + slot * p.kd + part * 8, ok);
-      else cp_async16(vd_ + key * LD + (part - kchunks) * 8, p.vcache + slot * p.vd + (part - kchunks) * 8, ok);
-    }
+    const int j = tile * KEYS + lk;
+    bool ok = j >= key_lo && j <= pos_hi;
+    const int pi = p.page_shift >= 0 ? j >> p.page_shift : j / p.page_size;
+    const int page = ok ? bt[pi] : -1;
+    ok = ok && page >= 0;
+    const long long slot = ok ? ((long long)page * p.nkv + g) * p.page_size + (j - pi * p.page_size) : 0;
+    const bf16* ksrc = p.kcache + slot * p.kd;
+    const bf16* vsrc = p.vcache + slot * p.vd;
+    bf16* kdst = Ks + (stage * KEYS + lk) * LD;
+    bf16* vdst = Vs + (stage * KEYS + lk) * LD;
+    for (int part = lh; part < kchunks; part += 2) cp_async16(kdst + part * 8, ksrc + part * 8, ok);
+    for (int part = lh; part < vchunks; part += 2) cp_async16(vdst + part * 8, vsrc + part * 8, ok);
   };
 
   // this thread's two rows
@@ -157,43 +170,56 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
 
     float sc[KEYS / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < KEYS / 8; ++nt) {
-      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-      const bf16* kr = kt + (nt * 8 + (lane >> 2)) * LD + (lane & 3) * 2;
+    for (int nt = 0; nt < KEYS / 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+    // one ldmatrix brings the key fragments of two tiles of 8 keys for 16 dimensions
+    const bf16* kr = kt + ((lane & 7) + (lane >> 4) * 8) * LD + ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int np = 0; np < KEYS / 16; ++np) {
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
         if (ks * 16 < p.kd) {
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + ks * 16);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8);
-          mma_bf16(sc[nt], qf[ks], b0, b1);
+          uint32_t kb[4];
+          ldmatrix_x4(kb, kr + np * 16 * LD + ks * 16);
+          mma_bf16(sc[2 * np], qf[ks], kb[0], kb[1]);
+          mma_bf16(sc[2 * np + 1], qf[ks], kb[2], kb[3]);
         }
       }
     }
-    // mask, scale into the log2 domain, running maximum
+    // mask (only where a row's edge crosses the tile), scale into the log2 domain, running maximum
     const int key0 = tile * KEYS;
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    const bool edge = !v0 || !v1 || key0 < max(st0, st1) || key0 + KEYS - 1 > min(pos0, pos1);
+    if (__any_sync(0xffffffffu, edge)) {
 #pragma unroll
-    for (int nt = 0; nt < KEYS / 8; ++nt) {
+      for (int nt = 0; nt < KEYS / 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int j = key0 + nt * 8 + (lane & 3) * 2 + e;
-        const float a = (v0 && j >= st0 && j <= pos0) ? sc[nt][e] * p.scale_log2 : -INFINITY;
-        const float c = (v1 && j >= st1 && j <= pos1) ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
-        sc[nt][e] = a; sc[nt][2 + e] = c;
-        mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, c);
+        for (int e = 0; e < 2; ++e) {
+          const int j = key0 + nt * 8 + (lane & 3) * 2 + e;
+          const float a = (v0 && j >= st0 && j <= pos0) ? sc[nt][e] * p.scale_log2 : -INFINITY;
+          const float c = (v1 && j >= st1 && j <= pos1) ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
+          sc[nt][e] = a; sc[nt][2 + e] = c;
+          mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, c);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < KEYS / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nt][e] *= p.scale_log2;
+        mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1])); mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
       }
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
     const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;     // a row that has seen nothing yet
-    const float c0 = exp2f(m0 - u0), c1 = exp2f(m1 - u1);
+    const float c0 = fast_exp2(m0 - u0), c1 = fast_exp2(m1 - u1);
     m0 = n0; m1 = n1;
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < KEYS / 8; ++nt) {
-      sc[nt][0] = exp2f(sc[nt][0] - u0); sc[nt][1] = exp2f(sc[nt][1] - u0);
-      sc[nt][2] = exp2f(sc[nt][2] - u1); sc[nt][3] = exp2f(sc[nt][3] - u1);
+      sc[nt][0] = fast_exp2(sc[nt][0] - u0); sc[nt][1] = fast_exp2(sc[nt][1] - u0);
+      sc[nt][2] = fast_exp2(sc[nt][2] - u1); sc[nt][3] = fast_exp2(sc[nt][3] - u1);
       s0 += sc[nt][0] + sc[nt][1]; s1 += sc[nt][2] + sc[nt][3];
     }
     s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
@@ -311,7 +337,8 @@ RLLM_API int rllm_sink_attention_mma(const void* q, long long q_stride, const vo
   if (tiles > 2147483647LL || nkv > 65535) return ERR_TOO_LARGE;
   Args a = {(const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, (bf16*)out, out_stride, positions, cu_q,
             block_table, bt_stride, num_seqs, nh, nkv, kd, vd, page_size, scale * 1.4426950408889634f, window, chunk, sinks,
-            gate, gate_ld, splits, pacc, pml};
+            gate, gate_ld, splits, pacc, pml, -1};
+  for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) a.page_shift = sft;
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 grid((unsigned)tiles, (unsigned)nkv, (unsigned)splits);
   const int dp = (kd <= 64 && vd <= 64) ? 64 : 128;
