@@ -12,7 +12,8 @@
 // and value zero. With `splits` > 1 the CTAs of grid.z share a tile's key tiles in fixed ranges and write
 // unnormalised parts (sum, maximum, denominator) that sink_attention_merge joins in range order; the sink goes
 // with the first range, the output gate with whoever writes the result. Head sizes are padded with zeros in
-// shared memory to DP (64 or 128) numbers.
+// shared memory to DP (64 or 128) numbers. Steps whose sequences bring at most 16 rows each (decoding) take the
+// FEW form of the kernel: see there.
 #pragma once
 
 namespace sinkmma {
@@ -71,7 +72,10 @@ __device__ __forceinline__ int first_key(int pos, int window, int chunk) {
   return start;
 }
 
-template <int DP>
+// FEW: the step's sequences bring at most 16 rows each (single tokens with up to 16 heads a kv head). The four warps
+// then all hold the tile's 16 rows and split each tile's 64 keys between them (16 keys a warp), each with a running
+// softmax of its own; the four are joined in warp order through shared memory at the end.
+template <int DP, bool FEW>
 __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args p) {
   pdl_launch();
   pdl_wait();
@@ -128,7 +132,9 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   };
 
   // this thread's two rows
-  const int r0 = row_base + warp * 16 + (lane >> 2), r1 = r0 + 8;
+  constexpr int NT = FEW ? 2 : KEYS / 8;           // tiles of 8 keys a warp takes of a tile of 64
+  const int kofs = FEW ? warp * 16 : 0;            // the first of them
+  const int r0 = row_base + (FEW ? 0 : warp * 16) + (lane >> 2), r1 = r0 + 8;
   const int t0l = r0 / Gq, t1l = r1 / Gq;
   const bool v0 = t0l < ql, v1 = t1l < ql;
   const int h0 = g * Gq + r0 % Gq, h1 = g * Gq + r1 % Gq;
@@ -153,7 +159,7 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   float o[DP / 8][4];
 #pragma unroll
   for (int i = 0; i < DP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const bool with_sink = p.sinks && z == 0;
+  const bool with_sink = p.sinks && z == 0 && (!FEW || warp == 0);
   float m0 = (with_sink && v0) ? p.sinks[h0] * 1.4426950408889634f : -INFINITY, l0 = (with_sink && v0) ? 1.f : 0.f;
   float m1 = (with_sink && v1) ? p.sinks[h1] * 1.4426950408889634f : -INFINITY, l1 = (with_sink && v1) ? 1.f : 0.f;
 
@@ -168,13 +174,13 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
     const bf16* kt = Ks + stage * KEYS * LD;
     const bf16* vt = Vs + stage * KEYS * LD;
 
-    float sc[KEYS / 8][4];
+    float sc[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < KEYS / 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
     // one ldmatrix brings the key fragments of two tiles of 8 keys for 16 dimensions
-    const bf16* kr = kt + ((lane & 7) + (lane >> 4) * 8) * LD + ((lane >> 3) & 1) * 8;
+    const bf16* kr = kt + (kofs + (lane & 7) + (lane >> 4) * 8) * LD + ((lane >> 3) & 1) * 8;
 #pragma unroll
-    for (int np = 0; np < KEYS / 16; ++np) {
+    for (int np = 0; np < NT / 2; ++np) {
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
         if (ks * 16 < p.kd) {
@@ -186,12 +192,12 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
       }
     }
     // mask (only where a row's edge crosses the tile), scale into the log2 domain, running maximum
-    const int key0 = tile * KEYS;
+    const int key0 = tile * KEYS + kofs;
     float mx0 = -INFINITY, mx1 = -INFINITY;
-    const bool edge = !v0 || !v1 || key0 < max(st0, st1) || key0 + KEYS - 1 > min(pos0, pos1);
+    const bool edge = !v0 || !v1 || key0 < max(st0, st1) || key0 + NT * 8 - 1 > min(pos0, pos1);
     if (__any_sync(0xffffffffu, edge)) {
 #pragma unroll
-      for (int nt = 0; nt < KEYS / 8; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int j = key0 + nt * 8 + (lane & 3) * 2 + e;
@@ -203,7 +209,7 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
       }
     } else {
 #pragma unroll
-      for (int nt = 0; nt < KEYS / 8; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) sc[nt][e] *= p.scale_log2;
         mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1])); mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
@@ -217,7 +223,7 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
     m0 = n0; m1 = n1;
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int nt = 0; nt < KEYS / 8; ++nt) {
+    for (int nt = 0; nt < NT; ++nt) {
       sc[nt][0] = fast_exp2(sc[nt][0] - u0); sc[nt][1] = fast_exp2(sc[nt][1] - u0);
       sc[nt][2] = fast_exp2(sc[nt][2] - u1); sc[nt][3] = fast_exp2(sc[nt][3] - u1);
       s0 += sc[nt][0] + sc[nt][1]; s1 += sc[nt][2] + sc[nt][3];
@@ -229,13 +235,13 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
     for (int i = 0; i < DP / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
     // O += P V
 #pragma unroll
-    for (int kk = 0; kk < KEYS / 16; ++kk) {
+    for (int kk = 0; kk < NT / 2; ++kk) {
       uint32_t pa[4];
       pa[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
       pa[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
       pa[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
       pa[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
-      const bf16* vr = vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8;
+      const bf16* vr = vt + (kofs + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8;
 #pragma unroll
       for (int np = 0; np < DP / 16; ++np) {
         if (np * 16 < p.vd) {
@@ -249,6 +255,52 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
     __syncthreads();          // the stage is free for the copy after next
   }
   cp_async_wait<0>();
+
+  if (FEW) {
+    // join the four warps' parts in warp order: warp w leaves its rows' sums, maxima and denominators in shared
+    // memory (the tiles are done with), then every warp takes a quarter of the columns' work
+    __syncthreads();
+    float* po = reinterpret_cast<float*>(smem_raw);          // [4][16][DP]
+    float* pm = po + 4 * 16 * DP;                            // [4][16], then the denominators [4][16]
+    float* pl = pm + 4 * 16;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = (lane >> 2) + half * 8;
+#pragma unroll
+      for (int i = 0; i < DP / 8; ++i)
+        *reinterpret_cast<float2*>(po + (warp * 16 + r) * DP + i * 8 + (lane & 3) * 2) = make_float2(o[i][half * 2], o[i][half * 2 + 1]);
+      if ((lane & 3) == 0) { pm[warp * 16 + r] = half ? m1 : m0; pl[warp * 16 + r] = half ? l1 : l0; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 16 * (p.vd / 2); idx += THREADS) {
+      const int r = idx / (p.vd / 2), c = (idx % (p.vd / 2)) * 2;
+      const int row = row_base + r, tl = row / Gq;
+      if (tl >= ql) continue;
+      const int h = g * Gq + row % Gq, t = q0 + tl;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, pm[w * 16 + r]);
+      float L = 0.f, a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        if (pm[w * 16 + r] == -INFINITY) continue;
+        const float f = fast_exp2(pm[w * 16 + r] - M);
+        L = fmaf(pl[w * 16 + r], f, L);
+        const float2 ov = *reinterpret_cast<const float2*>(po + (w * 16 + r) * DP + c);
+        a0 = fmaf(ov.x, f, a0); a1 = fmaf(ov.y, f, a1);
+      }
+      if (p.splits > 1) {
+        const size_t prow = ((size_t)t * p.nh + h) * p.splits + z;
+        *reinterpret_cast<float2*>(p.pacc + prow * p.vd + c) = make_float2(a0, a1);
+        if (c == 0) { p.pml[prow * 2] = M; p.pml[prow * 2 + 1] = L; }
+      } else {
+        float f = L > 0.f ? 1.f / L : 0.f;
+        if (p.gate) f *= 1.f / (1.f + __expf(-p.gate[(size_t)t * p.gate_ld + h]));
+        *reinterpret_cast<__nv_bfloat162*>(p.out + (size_t)t * p.out_stride + (size_t)h * p.vd + c) = __floats2bfloat162_rn(a0 * f, a1 * f);
+      }
+    }
+    return;
+  }
 
   if (p.splits > 1) {
     // unnormalised parts: [row = token * nh + head][split][vd], and (maximum, denominator)
@@ -342,17 +394,18 @@ RLLM_API int rllm_sink_attention_mma(const void* q, long long q_stride, const vo
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 grid((unsigned)tiles, (unsigned)nkv, (unsigned)splits);
   const int dp = (kd <= 64 && vd <= 64) ? 64 : 128;
-  const int smem = 4 * KEYS * (dp + 8) * (int)sizeof(bf16);
+  const int smem = 4 * KEYS * (dp + 8) * (int)sizeof(bf16);     // also holds the FEW join: 4 x 16 x (dp + 2) floats
+  const bool few = (long long)max_q_len * Gq <= 16;             // every sequence's rows fit one warp's 16
   int rc;
-  if (dp == 64) {
-    static bool done[64] = {};
-    if ((rc = allow_dynamic_smem(sink_attention_mma_kernel<64>, smem, done))) return rc;
-    rc = launch_ex(sink_attention_mma_kernel<64>, grid, dim3(THREADS), (size_t)smem, s, 1, a);
-  } else {
-    static bool done[64] = {};
-    if ((rc = allow_dynamic_smem(sink_attention_mma_kernel<128>, smem, done))) return rc;
-    rc = launch_ex(sink_attention_mma_kernel<128>, grid, dim3(THREADS), (size_t)smem, s, 1, a);
+#define GO(D, F)                                                                                     \
+  {                                                                                                  \
+    static bool done[64] = {};                                                                       \
+    if ((rc = allow_dynamic_smem(sink_attention_mma_kernel<D, F>, smem, done))) return rc;           \
+    rc = launch_ex(sink_attention_mma_kernel<D, F>, grid, dim3(THREADS), (size_t)smem, s, 1, a);     \
   }
+  if (dp == 64) { if (few) GO(64, true) else GO(64, false) }
+  else { if (few) GO(128, true) else GO(128, false) }
+#undef GO
   if (rc || splits == 1) return rc;
   const long long rows = (long long)n_tokens * nh;
   return launch_ex(sink_attention_merge_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, s, 1, (const float*)pacc,

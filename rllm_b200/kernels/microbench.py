@@ -10,6 +10,7 @@ ranges of keys) were tuned with, and the small case a profiler is pointed at.
     python -m rllm_b200.kernels.microbench latent-attn --heads 16 --rank 512 --rot 64 --tokens 2048
     python -m rllm_b200.kernels.microbench latent-attn --heads 16 --rank 512 --rot 64 --batch 8 --context 1024
     python -m rllm_b200.kernels.microbench gla --heads 16 --dim 128 --vdim 128 --tokens 2048 [--batch 8]
+    python -m rllm_b200.kernels.microbench sink --heads 32 --kv-heads 8 --dim 64 --vdim 48 --tokens 2048 --batch 8,64 --context 1024
     ... --plain 3      # no timing: three plain launches and a synchronize (for ncu -k ... -c ...)
 
 Timing: the kernel runs back to back over `--copies` distinct weight (or cache) tensors, larger
@@ -282,6 +283,70 @@ def cmd_gla(a) -> None:
             T * (cols * 2 + H * d * 4 + H * v * 4) + 2 * batch * H * d * v * 4, (5.0 if chunk == 0 else 8.0) * T * H * d * v)
 
 
+def cmd_sink(a) -> None:
+    """The kernels of attention with sink, gate and block mask and of layers that norm after the sum, each beside
+    the like kernel of plain grouped-query attention at the same sizes."""
+    from . import sink
+    nh, nkv, kd, vd, page, W = a.heads, a.kv_heads, a.dim, a.vdim, a.page, a.width
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    bf = lambda *shape: torch.randn(*shape, device=DEV, dtype=torch.bfloat16)
+    sinks, scale = torch.randn(nh, device=DEV), kd ** -0.5
+    for T in a.tokens:                                   # one prompt of T tokens
+        pages = (T + page - 1) // page
+        kc, vc, ve = bf(pages, nkv, page, kd), bf(pages, nkv, page, vd), bf(pages, nkv, page, kd)
+        bt, cu, lens = torch.arange(pages, device=DEV, dtype=torch.int32).view(1, pages), i32([0, T]), i32([T])
+        q, gate = bf(T, nh * kd), torch.randn(T, nh, device=DEV)
+        pos, seq = torch.arange(T, device=DEV, dtype=torch.int32), torch.zeros(T, device=DEV, dtype=torch.int32)
+        pairs = T * (T + 1) / 2
+        run([lambda: sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, None, a.chunk or None, sinks, gate)] * 4,
+            a.plain, f"sink attention (mma.sync) T={T} heads={nh}/{nkv} of {kd}/{vd}", flops=2.0 * nh * (kd + vd) * pairs)
+        if a.plain:
+            return
+        if kd in (64, 128):
+            out = torch.empty_like(q)
+            run([lambda: sm100.attention_fa(q, kc, ve, cu, lens, bt, T, T, T, nh, scale, None, splits=1, out=out)] * 4, 0,
+                f"  like: plain attention (mma.sync) T={T} heads of {kd}", flops=4.0 * nh * kd * pairs)
+            run([lambda: sm100.attention_prefill_tc(q, kc, ve, cu, lens, bt, T, nh, scale, None, out=out, chunk=a.chunk or None,
+                                                    sinks=sinks, gate=gate)] * 4, 0,
+                f"  equal head sizes: tcgen05 kernel with mask, sink and gate T={T}", flops=4.0 * nh * kd * pairs)
+        # query/key norm + rotation + cache write beside the plain rotation + cache write; sum-and-norm beside the plain norm
+        rot = kd // 2
+        proj = bf(T, (nh + nkv) * kd + nkv * vd)
+        wn, table = torch.ones(kd, device=DEV), torch.randn(T, rot // 2, 2, device=DEV)
+        slots = torch.arange(T, device=DEV, dtype=torch.int32)
+        run([lambda: sink.qk_norm_rope_store(proj, 0, nh * kd, (nh + nkv) * kd, nh, nkv, kd, vd, rot, wn, wn, 1e-6, table, slots,
+                                             kc, vc)] * 4, 0, f"query/key norm + rotation + cache write T={T}",
+            nbytes=proj.numel() * 2 + T * (nh * kd + nkv * (kd + vd)) * 2)
+        if kd in (64, 128):
+            qkv, inv = bf(T, (nh + 2 * nkv) * kd), torch.rand(kd // 2, device=DEV)
+            tb = ops.rope_table(pos, inv, T)
+            run([lambda: ops.rope_cache_write(qkv, pos, inv, slots, kc, ve, nh, nkv, kd, page, table=tb)] * 4, 0,
+                f"  like: rotation + cache write T={T}", nbytes=qkv.numel() * 2 + T * (nh + 2 * nkv) * kd * 2)
+        h, y, w = torch.randn(T, W, device=DEV), torch.randn(T, W, device=DEV), torch.ones(W, device=DEV)
+        copy = torch.empty(T, W, device=DEV, dtype=torch.bfloat16)
+        run([lambda: sink.postnorm(h, y, 2.0, w, 1e-6, copy=copy)] * 4, 0, f"sum + norm (float stream, bfloat16 copy) T={T} width={W}",
+            nbytes=T * W * 14)
+        run([lambda: ops.rmsnorm(h, w, 1e-6, torch.bfloat16, out=copy)] * 4, 0, f"  like: norm T={T}", nbytes=T * W * 6)
+    for B in a.batch:                                    # B single tokens at context C
+        C = a.context
+        pages = (C + page - 1) // page
+        copies = max(1, min(8, int(2e9 // (B * pages * nkv * page * (kd + vd) * 2))))
+        caches = [(bf(B * pages, nkv, page, kd), bf(B * pages, nkv, page, vd), bf(B * pages, nkv, page, kd)) for _ in range(copies)]
+        bt = torch.randperm(B * pages, device=DEV).to(torch.int32).view(B, pages).contiguous()
+        lens, pos, seq, cu = i32([C] * B), i32([C - 1] * B), torch.arange(B, device=DEV, dtype=torch.int32), torch.arange(B + 1, device=DEV, dtype=torch.int32)
+        q, gate = bf(B, nh * kd), torch.randn(B, nh, device=DEV)
+        tiles = B * nkv * ((nh // nkv + 63) // 64)
+        sp = max(1, min(16, 4 * sm100.init(DEV).sm_count // tiles, C // 128))
+        run([(lambda c=c: sink.sink_attention_mma(q, c[0], c[1], seq, pos, bt, cu, B, 1, nh, scale, None, a.chunk or None, sinks, gate,
+                                                  sp, C)) for c in caches], 0,
+            f"sink attention (mma.sync) {B} x 1 token, {C} keys, heads of {kd}/{vd}, ranges={sp}", nbytes=B * C * nkv * (kd + vd) * 2)
+        if kd in (64, 128):
+            out = torch.empty_like(q)
+            run([(lambda c=c: sm100.attention_decode(q, c[0], c[2], lens, bt, nh, scale, None, C, out=out)) for c in caches], 0,
+                f"  like: plain decode attention {B} x 1 token, {C} keys, heads of {kd}", nbytes=B * C * nkv * kd * 4)
+    sm100.check_error(DEV)
+
+
 def main(argv=None) -> int:
     ints = lambda s: [int(x) for x in s.split(",")]
     ap = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
@@ -315,6 +380,13 @@ def main(argv=None) -> int:
     p.add_argument("--copies", type=int, default=8)
     p.add_argument("--tokens", type=ints, default=[2048])
     for k, v in (("heads", 16), ("dim", 128), ("vdim", 128), ("batch", 0), ("chunk", 128)):
+        p.add_argument("--" + k, type=int, default=v)
+    p = sub.add_parser("sink")
+    p.add_argument("--plain", type=int, default=0, help="N plain launches of the prompt attention kernel instead of timing")
+    p.add_argument("--tokens", type=ints, default=[2048])
+    p.add_argument("--batch", type=ints, default=[8, 64])
+    for k, v in (("heads", 32), ("kv-heads", 8), ("dim", 64), ("vdim", 48), ("page", 16), ("context", 1024), ("chunk", 0),
+                 ("width", 2048)):
         p.add_argument("--" + k, type=int, default=v)
     for name in ("gemm", "attn-decode", "attn-prefill"):
         p = sub.add_parser(name)
@@ -352,7 +424,7 @@ def main(argv=None) -> int:
         print("microbench: no CUDA device", file=sys.stderr)
         return 1
     {"gemm": cmd_gemm, "attn-decode": cmd_attn_decode, "attn-prefill": cmd_attn_prefill, "sample": cmd_sample,
-     "experts": cmd_experts, "latent-attn": cmd_latent_attn, "gla": cmd_gla}[a.cmd](a)
+     "experts": cmd_experts, "latent-attn": cmd_latent_attn, "gla": cmd_gla, "sink": cmd_sink}[a.cmd](a)
     return 0
 
 
