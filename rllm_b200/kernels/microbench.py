@@ -385,7 +385,7 @@ def main(argv=None) -> int:
     p.add_argument("--plain", type=int, default=0, help="N plain launches of the prompt attention kernel instead of timing")
     p.add_argument("--tokens", type=ints, default=[2048])
     p.add_argument("--batch", type=ints, default=[8, 64])
-    for k, v in (("heads", 32), ("kv-heads", 8), ("dim", 64), ("vdim", 48), ("page", 16), ("context", 1024), ("chunk", 0),
+    for k, v in (("heads", 32), ("kv-heads", 8), ("dim", 64), ("vdim", 32), ("page", 16), ("context", 1024), ("chunk", 0),
                  ("width", 2048)):
         p.add_argument("--" + k, type=int, default=v)
     for name in ("gemm", "attn-decode", "attn-prefill"):
