@@ -432,6 +432,43 @@ def test_long_decoding_through_graphs(dirs, dtype, tol):
     check(got, {(k, i): want[k][i] for (k, i) in got}, tol, f"long decoding {dtype}", allow=0.0 if dtype == "float32" else 0.25)
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 6e-2)])
+def test_long_portions_over_pages_that_went_back(dirs, plain_long, dtype, tol):
+    """A prompt of 700 tokens in portions of 150: from the fourth portion on the layer with equal head sizes of
+    128 runs its long portions on the tcgen05 kernel over a block table whose pages before the current block of
+    100 positions have gone back to the pool; then 20 single tokens through graphs on the cluster kernel."""
+    from rllm_b200.engine import Entry, load_engine
+    from rllm_b200.kernels import sm100
+    toks, want = plain_long
+    eng = load_engine(dirs["LD"], dtype=dtype, page_size=16, max_tokens=768, max_requests=2)
+    got, at, calls = {}, 0, []
+    orig = sm100.attention_prefill_tc
+    sm100.attention_prefill_tc = lambda *a, **k: (calls.append(k.get("chunk")), orig(*a, **k))[1]
+    try:
+        for n in (150, 150, 150, 150, 80):
+            lg = eng.step([Entry("x", toks[at: at + n], list(range(n)))]).float().cpu().numpy()
+            got.update({("x", at + i): lg[i] for i in range(n)})
+            at += n
+            eng.cache.check()
+    finally:
+        sm100.attention_prefill_tc = orig
+    assert calls == ([100] if dtype == "bfloat16" else [])        # the fourth portion: 150 rows over 600 keys
+    for i in range(20):
+        got[("x", at)] = eng.step([Entry("x", [toks[at]], [0])]).float().cpu().numpy()[0]
+        at += 1
+    eng.check()
+    assert at == len(toks) and eng.graph_steps == 20
+    assert min(eng.cache.held_pages(eng.cache.live["x"])) <= (100 + 16) // 16 + 1
+    check(got, {("x", i): want[i] for i in range(len(toks))}, tol, f"long portions {dtype}", allow=0.0 if dtype == "float32" else 0.25)
+
+
+@pytest.fixture(scope="module")
+def plain_long(dirs):
+    cfg, w = P.read_model_dir(dirs["LD"])
+    toks = L.random_prompt(700, cfg["vocab"], 77)
+    return toks, P.forward(cfg, w, toks).numpy()
+
+
 @pytest.mark.parametrize("name", ["LB", "LC"])
 def test_greedy_generation_through_the_entry_point(dirs, name):
     """LLM.generate (scheduler, sampler, run-ahead decoding) against greedy decoding with the plain model."""
