@@ -142,6 +142,14 @@ class LivovikConfig(ModelConfig):
         layers = []
         for i, L in enumerate(layers_raw):
             where = f"layers[{i}]"
+            if isinstance(L, dict) and L.get("weights_of") is not None:
+                # an entry that names another layer's tensors may leave out what it shares with that layer
+                j, seen = L["weights_of"], {i}
+                while isinstance(j, int) and not isinstance(j, bool) and 0 <= j < len(layers_raw) and j not in seen \
+                        and isinstance(layers_raw[j], dict):
+                    seen.add(j)
+                    L = {**{k: v for k, v in layers_raw[j].items() if k != "weights_of"}, **L}
+                    j = layers_raw[j].get("weights_of")
             if not isinstance(L, dict) or L.get("type") != "attention":
                 raise ConfigError(f"{where}: 'type' must be 'attention', got {L.get('type') if isinstance(L, dict) else L!r}")
             mixer = SinkAttentionConfig.from_dict(_obj(L, "mixer", where), where + ".mixer")

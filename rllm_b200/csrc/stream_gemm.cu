@@ -79,6 +79,7 @@ struct Params {
   void* C;                  // output [T][N] (type by epilogue), row stride ldc
   long long ldc;
   int T;
+  int act;                  // store epilogue only: 1 stores max(value, 0)^2
   int njobs;
   int nchw;                 // chunks per warp and tile
   RopeArgs rope;
@@ -312,7 +313,7 @@ stream_gemm_kernel(const Params p) {
         }
       } else {
         const size_t o = (size_t)tok * p.ldc + job * 16 + r;
-        if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(s0);
+        if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(p.act ? fmaxf(s0, 0.f) * fmaxf(s0, 0.f) : s0);
         else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = s0;
         else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[o] += s0;
         else if (EPI == EPI_SWIGLU) ((bf16*)p.C)[o] = __float2bfloat16_rn(s0 / (1.f + expf(-s0)) * s1);
@@ -401,13 +402,15 @@ RLLM_API int rllm_stream_gemm_supported(int epi, int norm, int T, int N, int K, 
 RLLM_API int rllm_stream_gemm(int epi, const void* X, long long ldx, const float* h, long long ldh, const int* rows,
                               const void* g, int g_dt, float eps, const void* W, void* Cout, long long ldc,
                               int T, int N, int K, int sm_count, void* stream) {
-  if (epi < 0 || epi > EPI_SWIGLU) return ERR_BAD_SIZE;
+  const int act = epi >> 8;                       // as in rllm_tc_gemm: 0 | 1 << 8 stores max(value, 0)^2
+  epi &= 0xff;
+  if (epi < 0 || epi > EPI_SWIGLU || act > 1 || (act && epi != EPI_STORE)) return ERR_BAD_SIZE;
   const bool norm = X == nullptr;
   if (norm && (!h || !g || (g_dt != DT_F32 && g_dt != DT_BF16))) return ERR_BAD_SIZE;
   Params p = {};
   p.W = (const bf16*)W; p.N = N; p.K = K; p.up_row0 = N; p.x = (const bf16*)X; p.ldx = ldx;
   p.h = h; p.ldh = ldh; p.rows = rows; p.g = g; p.g_is_bf16 = g_dt == DT_BF16; p.eps = eps;
-  p.C = Cout; p.ldc = ldc; p.T = T;
+  p.C = Cout; p.ldc = ldc; p.T = T; p.act = act;
   return run(epi, norm, p, sm_count, (cudaStream_t)stream);
 }
 

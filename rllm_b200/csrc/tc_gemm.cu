@@ -154,14 +154,22 @@ struct Params {
   int splits;         // CTAs per cluster = ranges of K
   int bn;             // persistent kernel: tokens per tile (a multiple of 16, at most the template's BN)
   int* err;           // device error word (0 = fine)
+  int act;            // store epilogue only: 0 the value as it is, 1 max(value, 0)^2
   RopeArgs rope;
   NormArgs norm;      // NORM variants only
 };
 
+static thread_local int t_store_act = 0;     // host side: the activation of the call being launched (see StoreAct)
+
+__device__ __forceinline__ float store_act(const Params& p, float v) {
+  if (p.act) { v = fmaxf(v, 0.f); v *= v; }
+  return v;
+}
+
 template <int EPI>
 __device__ __forceinline__ void emit(const Params& p, int t, int n, float v, float u) {
   const size_t o = (size_t)t * p.ldc + n;
-  if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(v);
+  if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(store_act(p, v));
   else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v;
   else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[o] += v;
   else if (EPI == EPI_SWIGLU) ((bf16*)p.C)[o] = __float2bfloat16_rn(__fdividef(v, 1.f + __expf(-v)) * u);   // float, rounded once to bfloat16
@@ -1012,7 +1020,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
               bf16* cp = (bf16*)p.C + (size_t)(t0 + c0) * p.ldc + n;
 #pragma unroll
               for (int jj = 0; jj < CW; ++jj, cp += p.ldc)
-                if (c0 + jj < lim) *cp = __float2bfloat16_rn(__uint_as_float(g[jj]));
+                if (c0 + jj < lim) *cp = __float2bfloat16_rn(store_act(p, __uint_as_float(g[jj])));
             } else {
 #pragma unroll
               for (int jj = 0; jj < CW; ++jj) {
@@ -1466,6 +1474,7 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   else if ((rc = make_map(&mx, X, T, K, ldx, pair ? bn / 2 : bn))) return rc;
   Params p;
   p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits; p.err = err; p.bn = bn;
+  p.act = epi == EPI_STORE ? t_store_act : 0;
   p.rope = rope ? *rope : RopeArgs{};
   p.norm = norm ? *norm : NormArgs{};
   dim3 grid((T + bn - 1) / bn, (N + BM - 1) / BM, splits);
@@ -1527,12 +1536,20 @@ RLLM_API int rllm_tc_gemm_plan(int epi, int T, int N, int K, int sm_count, int a
 RLLM_API int rllm_tc_gemm_set_pairs(int on) { g_pairs = on != 0; return 0; }
 RLLM_API int rllm_tc_gemm_set_token_rows(int on) { g_token_rows = on != 0; return 0; }
 
+// The store epilogue (0) may carry an activation in the bits above the epilogue's number: epi = 0 | 1 << 8 stores
+// max(value, 0)^2. The launcher's own state for one call:
+struct StoreAct {
+  explicit StoreAct(int& epi) { t_store_act = (epi >> 8) == 1 && (epi & 0xff) == EPI_STORE; epi = (epi >> 8) > 1 ? -1 : (epi & 0xff); }
+  ~StoreAct() { t_store_act = 0; }
+};
+
 // X: [T, K] bf16, row stride ldx; W: [N, K] bf16 contiguous ([2N, K] for SwiGLU: gate rows then up
 // rows); C: [T, N] with row stride ldc, bf16 (store, SwiGLU) or float (store-float, accumulate).
 // allow_split 0: one CTA per output tile whatever the size; 1: the launcher's choice of ranges of K;
 // n > 1: n ranges where ranges are allowed. Returns 0, or a negative refusal.
 RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc,
                           int T, int N, int K, int allow_split, int* err, int sm_count, void* stream) {
+  const StoreAct sa(epi);
   if (epi < 0 || epi > 3 || !X) return ERR_BAD_SIZE;
   return run(epi, X, ldx, nullptr, W, Cout, ldc, T, N, K, allow_split, err, sm_count, nullptr, stream);
 }
@@ -1544,6 +1561,7 @@ RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, 
 RLLM_API int rllm_tc_gemm_norm(int epi, const float* h, long long ldh, const int* rows, const void* g, int g_dt,
                                float eps, const void* W, void* Cout, long long ldc, int T, int N, int K,
                                int allow_split, int* err, int sm_count, void* stream) {
+  const StoreAct sa(epi);
   if (epi < 0 || epi > 3 || epi == EPI_ACCUM_F32 || !h || !g || (g_dt != DT_F32 && g_dt != DT_BF16)) return ERR_BAD_SIZE;
   NormArgs nm;
   nm.h = h; nm.ldh = ldh; nm.rows = rows; nm.g = g; nm.g_is_bf16 = g_dt == DT_BF16; nm.eps = eps;

@@ -280,7 +280,12 @@ class Backend:
         """act(x W^T) in the run dtype; act "relu2" = max(., 0)^2."""
         if act != "relu2":
             raise ops.KernelError(f"activation {act!r} has no kernel")
-        return self._sink.relu2_(self.linear(x, w, tag="up"))
+        x = x.tensor() if isinstance(x, Normed) else x
+        if self._tc(x, w) and os.environ.get("RLLM_B200_NO_ACT_FUSION") != "1":
+            return self._sm100.gemm(x, w, ops.EPI_STORE, relu2=True)        # in the product's store epilogue
+        if self._tc(x, w):
+            return self._sink.relu2_(self._sm100.gemm(x, w, ops.EPI_STORE))
+        return self._sink.relu2_(ops.gemm_simt(x, w, ops.EPI_STORE))
 
     def qk_norm_rope_store(self, proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table, cache):
         writes = cache.writes

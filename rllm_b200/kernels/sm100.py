@@ -124,10 +124,17 @@ def plan(epilogue: int, T: int, N: int, K: int, device="cuda:0", split: bool | i
     return bn.value, sp.value
 
 
+ACT_RELU2 = 1 << 8          # added to the store epilogue's number: max(value, 0)^2 is stored
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | None = None,
-         split: bool = True) -> torch.Tensor:
+         split: bool = True, relu2: bool = False) -> torch.Tensor:
     """C = X W^T on the tensor cores. x [T, K] bf16 (unit inner stride); w [N, K] bf16 ([2N, K] with
-    the SwiGLU epilogue). `out` is required for the accumulate epilogue (the float residual)."""
+    the SwiGLU epilogue). `out` is required for the accumulate epilogue (the float residual). `relu2`
+    (store epilogue only): max(., 0)^2 of the float result is what is rounded and stored."""
+    if relu2 and epilogue != ops.EPI_STORE:
+        raise ops.KernelError("tc gemm: relu^2 goes with the store epilogue only")
+    code = epilogue | (ACT_RELU2 if relu2 else 0)
     if not gemm_supported(x, w):
         raise ops.KernelError("tc gemm: operands must be bfloat16, K a multiple of 8, 16-byte aligned")
     st = init(x.device)
@@ -142,12 +149,12 @@ def gemm(x: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | No
         raise ops.KernelError(f"tc gemm out must be [{T}, {N}] of {out_dtype}")
     if split and stream_supported(epilogue, False, T, N, K):
         rc = ops._fn("sm100", "rllm_stream_gemm")(
-            epilogue, x.data_ptr(), x.stride(0), None, 0, None, None, 0, 0.0, w.data_ptr(), out.data_ptr(),
+            code, x.data_ptr(), x.stride(0), None, 0, None, None, 0, 0.0, w.data_ptr(), out.data_ptr(),
             out.stride(0), T, N, K, st.sm_count, ops._stream())
         ops._check(rc, "stream_gemm")
         return out
     rc = ops._fn("sm100", "rllm_tc_gemm")(
-        epilogue, x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K,
+        code, x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K,
         int(split), st.err.data_ptr(), st.sm_count, ops._stream())
     ops._check(rc, "tc_gemm")
     return out

@@ -65,7 +65,7 @@ LC = {  # nothing a multiple of 8: width 100, vocabulary 77, heads of 20 and 12 
 }
 LD = {  # head sizes the tensor-core kernel takes (64 / 128 / 16 numbers), 16 query heads a kv head, masks at and across tile borders
     "architecture": "Livovik", "vocab": 96, "width": 128, "norm": {"eps": 1e-6}, "postln_alpha": 2.5,
-    "layers": [layer(attn(16, 1, 64, 32, 0.125, rot(250000.0, 32, (4.0, 1.0, 4.0, 128)), 64), dense(64)),
+    "layers": [layer(attn(16, 1, 64, 32, 0.11, rot(300000.0, 32, (6.0, 1.0, 3.0, 128)), 64), dense(64)),
                layer(attn(2, 2, 128, 128, 0.09, rot(10000.0, 128), 100), moe(32, 8, 2, shared=16)),
                layer(attn(8, 4, 16, 16, 0.25, rot(10000.0, 8), None), None)],
 }

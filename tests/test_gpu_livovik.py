@@ -100,7 +100,7 @@ MIXERS = [
     (L.attn(6, 1, 24, 40, 0.17, L.rot(1e6, 8), 3), 8),                                # blocks shorter than a page, one kv head
     (L.attn(2, 2, 48, 48, 0.125, None, None), 8),                                     # no rotation, no mask
     (L.attn(3, 1, 20, 12, 0.25, L.rot(10000.0, 20, (4.0, 1.0, 2.0, 32)), 33), 16),    # nothing a multiple of 8
-    (L.attn(16, 1, 64, 32, 0.125, L.rot(250000.0, 32, (4.0, 1.0, 4.0, 128)), 64), 16),  # a token's heads fill a row tile
+    (L.attn(16, 1, 64, 32, 0.11, L.rot(300000.0, 32, (6.0, 1.0, 3.0, 128)), 64), 16),  # a token's heads fill a row tile
     (L.attn(2, 2, 128, 128, 0.09, L.rot(10000.0, 128), 50), 16),                      # the largest head size
     (L.attn(8, 4, 16, 16, 0.25, L.rot(10000.0, 8), 1), 4),                            # a block of one position: the query alone
 ]
@@ -256,6 +256,21 @@ def test_product_with_a_few_weight_rows(dtype, N, K):
     x, w = rnd(21, K, seed=1).to(DT[dtype]), rnd(N, K, seed=2).to(DT[dtype])
     got = ops.gemm_skinny(x.to(DEV), w.to(DEV))
     assert got.dtype == torch.float32 and rel(got, x.double() @ w.double().T) < 3e-6
+
+
+@pytest.mark.parametrize("T", [1, 8, 9, 40, 64, 130, 300, 2048])
+@pytest.mark.parametrize("N,K", [(512, 256), (1536, 512)])
+def test_relu_squared_in_the_store_epilogue_of_the_products(T, N, K):
+    """Every kernel a step's size selects (weight streaming up to 8 tokens, tcgen05 small tiles with ranges of K
+    merged in a cluster, the persistent kernel) stores max(., 0)^2 of the float result."""
+    from rllm_b200.kernels import ops, sm100
+    x, w = rnd(T, K, seed=T).bfloat16(), rnd(N, K, seed=N, scale=0.1).bfloat16()
+    want = torch.relu(x.double() @ w.double().T) ** 2
+    got = sm100.gemm(x.to(DEV), w.to(DEV), ops.EPI_STORE, relu2=True)
+    assert got.dtype == torch.bfloat16 and rel(got, want) < 1e-2
+    plain = sm100.gemm(x.to(DEV), w.to(DEV), ops.EPI_STORE)          # the switch leaves nothing behind
+    assert rel(plain, x.double() @ w.double().T) < 1e-2 and float(plain.min()) < 0
+    sm100.check_error(DEV)
 
 
 def test_long_row_lists_of_gated_experts_run_on_tcgen05():

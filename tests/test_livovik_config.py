@@ -70,6 +70,14 @@ def test_refusals(edit, what):
     assert what.split(".")[-1] in str(e.value)
 
 
+def test_an_entry_on_another_layers_tensors_may_leave_out_what_it_shares():
+    raw = copy.deepcopy(L.LC)
+    full = config_from_dict(raw)[1]
+    raw["layers"][1] = {"type": "attention", "weights_of": 0, "mixer": raw["layers"][1]["mixer"]}      # no mlp key
+    raw["layers"][3] = {"weights_of": 1}                                                                   # nothing else
+    assert config_from_dict(raw)[1] == full
+
+
 def test_random_folder_is_read_by_the_plain_reader(tmp_path):
     d = L.make_model_dir(tmp_path, "LB")
     cfg, w = P.read_model_dir(d)
