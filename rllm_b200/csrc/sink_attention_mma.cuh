@@ -6,7 +6,7 @@
 // with 16 heads a kv head fills a warp's 16 rows. Which sequence and tile a CTA has it finds from the row
 // ranges on the device (the grid is the step's upper bound of tiles), so nothing of the launch depends on
 // what the host cannot know when a decode graph is captured. Keys come in tiles of 64, aligned to 64 from
-// position 0, copied through the block table by `cp.async` (16 bytes a copy, two tiles in flight); only the
+// position 0, copied through the block table by `cp.async` (16 bytes a copy, one tile in flight beside the one at work); only the
 // tiles between the first key any row sees (window and block rule) and the last row's own position are
 // walked, keys outside a row's mask get -inf. The sink opens a row's running softmax as a key of score `sink`
 // and value zero. With `splits` > 1 the CTAs of grid.z share a tile's key tiles in fixed ranges and write
@@ -18,7 +18,7 @@
 
 namespace sinkmma {
 
-constexpr int ROWS = 64, KEYS = 64, THREADS = 128;
+constexpr int ROWS = 64, KEYS = 64, THREADS = 128, STAGES = 2;      // three stages measured level with two
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -81,21 +81,39 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   pdl_wait();
   constexpr int LD = DP + 8;                       // padded row of a key or value tile, in elements
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);    // [2][KEYS][LD]
-  bf16* Vs = Ks + 2 * KEYS * LD;                   // [2][KEYS][LD]
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);    // [STAGES][KEYS][LD]
+  bf16* Vs = Ks + STAGES * KEYS * LD;              // [STAGES][KEYS][LD]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int Gq = p.nh / p.nkv, g = blockIdx.y, z = blockIdx.z;
 
-  // which sequence, which tile of its rows
-  int b = blockIdx.x, s = 0, q0 = 0, ql = 0;
-  for (; s < p.num_seqs; ++s) {
-    q0 = p.cu_q[s];
-    ql = p.cu_q[s + 1] - q0;
-    const int nt = (ql * Gq + ROWS - 1) / ROWS;
-    if (b < nt) break;
-    b -= nt;
+  // which sequence, which tile of its rows. FEW: every sequence has one tile. Else 32 sequences a round: each lane
+  // counts one sequence's tiles, a warp scan finds the one that holds tile blockIdx.x (every warp for itself).
+  int b = blockIdx.x, s = -1;
+  if (FEW) {
+    if (b < p.num_seqs) { s = b; b = 0; }
+  } else {
+    int base = 0;
+    for (int s0 = 0; s0 < p.num_seqs; s0 += 32) {
+      const int i = s0 + lane;
+      const int nt = i < p.num_seqs ? ((p.cu_q[i + 1] - p.cu_q[i]) * Gq + ROWS - 1) / ROWS : 0;
+      int inc = nt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      const int total = __shfl_sync(0xffffffffu, inc, 31);
+      if (b < base + total) {
+        const int l = __ffs(__ballot_sync(0xffffffffu, b < base + inc)) - 1;
+        s = s0 + l;
+        b -= base + __shfl_sync(0xffffffffu, inc - nt, l);
+        break;
+      }
+      base += total;
+    }
   }
-  if (s >= p.num_seqs) return;
+  if (s < 0) return;
+  const int q0 = p.cu_q[s], ql = p.cu_q[s + 1] - q0;
   const int row_base = b * ROWS;
   const int tok_lo = row_base / Gq, tok_hi = min(ql - 1, (row_base + ROWS - 1) / Gq);
   const int pos_lo = p.positions[q0 + tok_lo], pos_hi = p.positions[q0 + tok_hi];
@@ -108,8 +126,11 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   }
   const int* bt = p.block_table + (size_t)s * p.bt_stride;
 
-  // zero the tiles once: the columns beyond kd / vd are never copied into
-  for (int i = tid; i < 4 * KEYS * LD / 8; i += THREADS) reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
+  // zero the tiles once where a head is narrower than DP: the columns beyond kd / vd are never copied into
+  if (p.kd < DP)
+    for (int i = tid; i < STAGES * KEYS * LD / 8; i += THREADS) reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0, 0, 0, 0);
+  if (p.vd < DP)
+    for (int i = tid; i < STAGES * KEYS * LD / 8; i += THREADS) reinterpret_cast<uint4*>(Vs)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
 
   const int kchunks = p.kd / 8, vchunks = p.vd / 8;
@@ -163,13 +184,18 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   float m0 = (with_sink && v0) ? p.sinks[h0] * 1.4426950408889634f : -INFINITY, l0 = (with_sink && v0) ? 1.f : 0.f;
   float m1 = (with_sink && v1) ? p.sinks[h1] * 1.4426950408889634f : -INFINITY, l1 = (with_sink && v1) ? 1.f : 0.f;
 
-  if (tile0 < tile1) load_tile(tile0, 0);
-  cp_async_commit();
-  for (int tile = tile0; tile < tile1; ++tile) {
-    const int stage = (tile - tile0) & 1;
-    if (tile + 1 < tile1) load_tile(tile + 1, stage ^ 1);
+  // STAGES - 1 tiles are on their way while one is worked on (a commit per tile, empty past the end, so that
+  // the count of groups in flight says which tile has landed)
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (tile0 + i < tile1) load_tile(tile0 + i, i);
     cp_async_commit();
-    cp_async_wait<1>();
+  }
+  for (int tile = tile0; tile < tile1; ++tile) {
+    const int stage = (tile - tile0) % STAGES;
+    if (tile + STAGES - 1 < tile1) load_tile(tile + STAGES - 1, (tile - tile0 + STAGES - 1) % STAGES);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
     const bf16* kt = Ks + stage * KEYS * LD;
     const bf16* vt = Vs + stage * KEYS * LD;
@@ -252,7 +278,7 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
         }
       }
     }
-    __syncthreads();          // the stage is free for the copy after next
+    __syncthreads();          // the stage is free for the next iteration's copy
   }
   cp_async_wait<0>();
 
@@ -394,7 +420,7 @@ RLLM_API int rllm_sink_attention_mma(const void* q, long long q_stride, const vo
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 grid((unsigned)tiles, (unsigned)nkv, (unsigned)splits);
   const int dp = (kd <= 64 && vd <= 64) ? 64 : 128;
-  const int smem = 4 * KEYS * (dp + 8) * (int)sizeof(bf16);     // also holds the FEW join: 4 x 16 x (dp + 2) floats
+  const int smem = 2 * STAGES * KEYS * (dp + 8) * (int)sizeof(bf16);     // also holds the FEW join: 4 x 16 x (dp + 2) floats
   const bool few = (long long)max_q_len * Gq <= 16;             // every sequence's rows fit one warp's 16
   int rc;
 #define GO(D, F)                                                                                     \
