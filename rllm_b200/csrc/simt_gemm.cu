@@ -6,8 +6,8 @@
 // in ascending order by one thread, so a row's result does not depend on which
 // other rows share the batch.
 //
-// Epilogues: store (activation type), store float (logits), accumulate into the
-// float residual stream, and SwiGLU over a gate/up pair of weight tiles
+// Epilogues: store (activation type), store max(., 0)^2 (activation type), store float (logits),
+// accumulate into the float residual stream, and SwiGLU over a gate/up pair of weight tiles
 // (W holds [2N, K]: gate rows first, up rows after; out[t, n] = silu(g) * u).
 // Reference counterparts: src/gpu/cuda/shaders/matmul.cu:49-77, 216-248 and
 // moe.cu:86-147 (fused gate-up).
@@ -18,7 +18,7 @@ namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;   // 256 threads, 4x4 outputs each
 
-enum : int { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU = 3 };
+enum : int { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU = 3, EPI_RELU2 = 4 };
 
 template <typename TI, int EPI>
 __global__ void __launch_bounds__(256)
@@ -86,6 +86,7 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, void* __res
       if (EPI == EPI_STORE) ((TI*)Cv)[o] = from_f32<TI>(v);
       else if (EPI == EPI_STORE_F32) ((float*)Cv)[o] = v;
       else if (EPI == EPI_ACCUM_F32) ((float*)Cv)[o] += v;
+      else if (EPI == EPI_RELU2) { const float r = fmaxf(v, 0.f); ((TI*)Cv)[o] = from_f32<TI>(r * r); }   // squared in float, rounded once
       else { float g = v, uu = acu[DUAL ? i : 0][j]; ((TI*)Cv)[o] = from_f32<TI>(g / (1.f + expf(-g)) * uu); }
     }
   }
@@ -102,6 +103,7 @@ int launch(int epi, const void* A, const void* W, void* C, const void* bias, int
     case EPI_STORE_F32: GO(EPI_STORE_F32); break;
     case EPI_ACCUM_F32: GO(EPI_ACCUM_F32); break;
     case EPI_SWIGLU: GO(EPI_SWIGLU); break;
+    case EPI_RELU2: GO(EPI_RELU2); break;
     default: return ERR_BAD_SIZE;
   }
 #undef GO

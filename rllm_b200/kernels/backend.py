@@ -285,7 +285,7 @@ class Backend:
             return self._sm100.gemm(x, w, ops.EPI_STORE, relu2=True)        # in the product's store epilogue
         if self._tc(x, w):
             return self._sink.relu2_(self._sm100.gemm(x, w, ops.EPI_STORE))
-        return self._sink.relu2_(ops.gemm_simt(x, w, ops.EPI_STORE))
+        return ops.gemm_simt(x, w, ops.EPI_RELU2)
 
     def qk_norm_rope_store(self, proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table, cache):
         writes = cache.writes

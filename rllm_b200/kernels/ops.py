@@ -17,6 +17,7 @@ DT_F32, DT_BF16 = 0, 1
 _DT = {torch.float32: DT_F32, torch.bfloat16: DT_BF16}
 
 EPI_STORE, EPI_STORE_F32, EPI_ACCUM_F32, EPI_SWIGLU = 0, 1, 2, 3
+EPI_RELU2 = 4          # the CUDA-core product only: max(., 0)^2 of the float result, stored in the operand type
 
 _ERR = {-1: "unsupported dtype", -2: "unsupported size", -3: "misaligned operand",
         -4: "problem too large for this kernel", -5: "kernel set-up failed"}
@@ -248,7 +249,8 @@ def silu_gate(gu: torch.Tensor) -> torch.Tensor:
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | None = None,
               bias: torch.Tensor | None = None) -> torch.Tensor:
-    """C = A W^T on the CUDA cores (float accumulate). a [T, K]; w [N, K] ([2N, K] for SwiGLU)."""
+    """C = A W^T on the CUDA cores (float accumulate). a [T, K]; w [N, K] ([2N, K] for SwiGLU). Epilogue
+    EPI_RELU2 stores max(C, 0)^2 in a's dtype."""
     _cuda(a, "a"); _cuda(w, "w")
     if a.dim() != 2 or w.dim() != 2 or a.stride(1) != 1 or not w.is_contiguous():
         raise KernelError("gemm takes a [T, K] (unit inner stride) and a contiguous w [N, K]")

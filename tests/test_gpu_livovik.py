@@ -60,6 +60,10 @@ def test_activations(dtype):
         assert rel(sink.gated_act(gb.to(DEV), torch.bfloat16), want) < 8e-3
     x = rnd(50, 33, seed=3).to(DT[dtype])
     assert rel(sink.relu2_(x.to(DEV).clone()), torch.relu(x.double()) ** 2) < (1e-6 if dtype == "float32" else 8e-3)
+    from rllm_b200.kernels import ops
+    w = rnd(21, 33, seed=4).to(DT[dtype])            # the CUDA-core product squares in float and rounds once
+    got = ops.gemm_simt(x.to(DEV), w.to(DEV), ops.EPI_RELU2)
+    assert got.dtype == DT[dtype] and rel(got, torch.relu(x.double() @ w.double().T) ** 2) < (2e-6 if dtype == "float32" else 6e-3)
 
 
 @pytest.mark.parametrize("E,top", [(8, 1), (6, 2), (7, 3), (64, 8), (4, 4)])
